@@ -32,10 +32,13 @@ class StoreSizes:
 @dataclass(frozen=True)
 class KVSpec:
     """Keys and values of ``n_kv_heads`` heads of ``head_dim`` for every token
-    (``window`` None) or for the last ``window`` tokens."""
+    (``window`` None) or for the last ``window`` tokens.  ``values_in_keys``: a
+    token's value is read from its key row (a latent that serves as both), so the
+    store holds one tensor and hands it out as keys and as values."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    values_in_keys: bool = False
 
     def make_store(self, n_layers: int, sizes: StoreSizes, dtype, device, allocate: bool = True):
         from .stores import KVStore

@@ -63,7 +63,7 @@ class KVStore:
             # kernel, but a tensor-core product of probability 0 with a NaN that
             # happened to be in fresh memory would still be NaN
             self.k = torch.zeros(shape, dtype=dtype, device=self.device)
-            self.v = torch.zeros(shape, dtype=dtype, device=self.device)
+            self.v = self.k if spec.values_in_keys else torch.zeros(shape, dtype=dtype, device=self.device)
             self.table_dev = torch.zeros((max_slots, max_pages_per_seq), dtype=torch.int32,
                                          device=self.device)
 

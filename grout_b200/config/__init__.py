@@ -3,9 +3,10 @@ from .generation import GenerationConfig
 from .qwen3 import Qwen3Config
 from .suvazen import SuvazenConfig
 from .sonalorn import SonalornConfig
+from .zutazen import ZutazenConfig
 from .registry import (Architecture, known_architectures, load_config, register_architecture,
                        resolve_architecture, unregister_architecture)
 
-__all__ = ["ConfigError", "ModelConfig", "GenerationConfig", "Qwen3Config", "SuvazenConfig", "SonalornConfig", "Architecture",
+__all__ = ["ConfigError", "ModelConfig", "GenerationConfig", "Qwen3Config", "SuvazenConfig", "SonalornConfig", "ZutazenConfig", "Architecture",
            "known_architectures", "load_config", "register_architecture",
            "resolve_architecture", "unregister_architecture", "read_json"]

@@ -8,8 +8,9 @@
 // out[r, i] = g / (1 + exp(-g)) * u in 32-bit, one rounding at the store
 // (the reference's silu_mul_2d_f16, src/kernels.rs:271-296).
 // The gate's activation: 0 = silu, g / (1 + exp(-g)); 1 = the tanh form of gelu,
-// 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))).
+// 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))); 2 = relu.
 template <int ACT> __device__ __forceinline__ float gate_act(float g) {
+  if (ACT == 2) return fmaxf(g, 0.f);
   if (ACT == 1) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
   return g / (1.0f + expf(-g));
 }
@@ -93,6 +94,13 @@ GB_EXPORT int gb_gelu_tanh_mul_f32(const void* in, void* out, int n_rows, int I,
 GB_EXPORT int gb_gelu_tanh_mul_bf16(const void* in, void* out, int n_rows, int I, int group,
                                     cudaStream_t s) {
   return silu_mul<bf16, 1>(in, out, n_rows, I, group, s);
+}
+// The same with relu as the gate's activation.
+GB_EXPORT int gb_relu_mul_f32(const void* in, void* out, int n_rows, int I, int group, cudaStream_t s) {
+  return silu_mul<float, 2>(in, out, n_rows, I, group, s);
+}
+GB_EXPORT int gb_relu_mul_bf16(const void* in, void* out, int n_rows, int I, int group, cudaStream_t s) {
+  return silu_mul<bf16, 2>(in, out, n_rows, I, group, s);
 }
 
 template <typename TI, typename TO>
@@ -200,4 +208,63 @@ GB_EXPORT int gb_scale_softcap_f32(float* x, long long n, float scale, float cap
   if (n == 0) return 0;
   return gb_launch(scale_softcap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, x,
                    (size_t)n, scale, cap);
+}
+
+// A gated feed-forward's inner step with biases, on the 32-bit sums of the fused gate|up
+// product: out[r, i] = act(g + bias_g) * (u + bias_u), rounded once.  `in` [n_rows, 2 I] and
+// `bias` [2 I] have the same layout (plain or in groups, as silu_mul's).
+template <typename T, int ACT>
+__global__ void bias_gate_mul_kernel(const float* in, const float* __restrict__ bias, T* __restrict__ out,
+                                     int I, int group) {
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  const size_t r = blockIdx.y;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= I) return;
+  const int gi = group ? (i / group) * 2 * group + (i % group) : i;
+  const int ui = group ? gi + group : I + i;
+  const float g = in[r * 2 * I + gi] + bias[gi];
+  const float u = in[r * 2 * I + ui] + bias[ui];
+  pdl_launch_dependents_if_large();
+  out[r * I + i] = from_f32<T>(gate_act<ACT>(g) * u);
+}
+template <typename T>
+static int bias_gate_mul(const float* in, const float* bias, void* out, int n_rows, int I, int group,
+                         int act, cudaStream_t s) {
+  if (n_rows < 0 || I <= 0 || group < 0 || (group && I % group) || act < 0 || act > 2 || !in || !bias || !out)
+    return GB_ERR_BAD_ARG;
+  for (int r0 = 0; r0 < n_rows; r0 += 65535) {      // rows go to grid.y
+    const int n = n_rows - r0 < 65535 ? n_rows - r0 : 65535;
+    const dim3 grid((I + 255) / 256, n);
+    const float* src = in + (size_t)r0 * 2 * I;
+    T* dst = (T*)out + (size_t)r0 * I;
+    int e = act == 0 ? gb_launch(bias_gate_mul_kernel<T, 0>, grid, dim3(256), 0, s, src, bias, dst, I, group)
+          : act == 1 ? gb_launch(bias_gate_mul_kernel<T, 1>, grid, dim3(256), 0, s, src, bias, dst, I, group)
+                     : gb_launch(bias_gate_mul_kernel<T, 2>, grid, dim3(256), 0, s, src, bias, dst, I, group);
+    if (e) return e;
+  }
+  return 0;
+}
+GB_EXPORT int gb_bias_gate_mul_f32(const float* in, const float* bias, void* out, int n_rows, int I,
+                                   int group, int act, cudaStream_t s) {
+  return bias_gate_mul<float>(in, bias, out, n_rows, I, group, act, s);
+}
+GB_EXPORT int gb_bias_gate_mul_bf16(const float* in, const float* bias, void* out, int n_rows, int I,
+                                    int group, int act, cudaStream_t s) {
+  return bias_gate_mul<bf16>(in, bias, out, n_rows, I, group, act, s);
+}
+
+// x[r, :] += bias in place on 32-bit rows: a projection's bias added to its 32-bit sums.
+__global__ void add_bias_kernel(float* x, const float* __restrict__ bias, size_t n, int N) {
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  x[i] += bias[i % N];
+}
+GB_EXPORT int gb_add_bias_f32(float* x, const float* bias, long long n_rows, int N, cudaStream_t s) {
+  if (n_rows < 0 || N <= 0 || !x || !bias) return GB_ERR_BAD_ARG;
+  if (n_rows == 0) return 0;
+  const size_t n = (size_t)n_rows * N;
+  return gb_launch(add_bias_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, x, bias, n, N);
 }

@@ -100,3 +100,35 @@ GB_EXPORT int gb_embed_pos_norm_bf16(const void* table, const void* positions, c
                                      int n_tokens, int H, int V, int P, cudaStream_t s) {
   return embed_pos_norm_launch<bf16>(table, positions, ids, pos, w, eps, out, n_tokens, H, V, P, s);
 }
+
+// Token embedding times a constant: out[t, :] = scale * table[ids[t], :] as 32-bit rows,
+// which are the residual stream itself (a scaled row need not be a bfloat16 number).
+template <typename T>
+__global__ void embed_scaled_kernel(const T* __restrict__ table, const int* ids, float scale,
+                                    float* __restrict__ out, int H, int V) {
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  const bool ok = id >= 0 && id < V;  // an id outside the table gives a zero row
+  const T* src = table + (size_t)(ok ? id : 0) * H;
+  float* dst = out + (size_t)t * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = ok ? scale * to_f32<T>(src[i]) : 0.f;
+  pdl_launch_dependents_if_large();
+}
+template <typename T>
+static int embed_scaled_launch(const void* table, const int* ids, float scale, float* out, int n_tokens,
+                               int H, int V, cudaStream_t stream) {
+  if (n_tokens < 0 || H <= 0 || V <= 0) return GB_ERR_BAD_ARG;
+  if (n_tokens == 0) return 0;
+  return gb_launch(embed_scaled_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (const T*)table, ids,
+                   scale, out, H, V);
+}
+GB_EXPORT int gb_embed_scaled_f32(const void* table, const int* ids, float scale, float* out,
+                                  int n_tokens, int H, int V, cudaStream_t s) {
+  return embed_scaled_launch<float>(table, ids, scale, out, n_tokens, H, V, s);
+}
+GB_EXPORT int gb_embed_scaled_bf16(const void* table, const int* ids, float scale, float* out,
+                                   int n_tokens, int H, int V, cudaStream_t s) {
+  return embed_scaled_launch<bf16>(table, ids, scale, out, n_tokens, H, V, s);
+}

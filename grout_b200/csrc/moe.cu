@@ -10,6 +10,13 @@
 //   output >= E:    an expert that hands its input on, y = x
 //   out = sum over the chosen of s * y
 //
+// Each of these terms is an argument.  `score_fn` 1 takes s = sigmoid(z), every output
+// by itself, instead of the softmax; `correction` may be null (no correction); a limit
+// of +inf clamps nothing; `up_offset` is the 1 in (u + 1) and may be 0; with
+// `weigh_input` the weight multiplies the expert's input instead of its result,
+// y = expert(s x): gate and up have no bias, so their 32-bit sums are multiplied by s
+// before the activation, and the second product is stored as it is.
+//
 // Nothing here needs the host to know how many tokens an expert got, so a step
 // can be captured: `route` chooses and counts, and its last block turns the counts into a
 // list of (token, choice) pairs ordered by expert; the two products walk
@@ -38,6 +45,9 @@ struct MoeArgs {
   float* out;               // [top, T, W]
   int T, W, F, E, n_identity, top, n_groups, keep_groups;
   float limit, slope;
+  int score_fn;              // 0: softmax over the outputs, 1: sigmoid of each
+  int weigh_input;           // the weight multiplies the expert's input, not its result
+  float up_offset;           // y = act(g) (u + up_offset)
 };
 
 #define MOE_MAX_OUTPUTS 1024
@@ -88,9 +98,14 @@ __global__ void __launch_bounds__(MOE_ROUTE_THREADS) moe_route_kernel(const MoeA
   }
   if (tid == 0) {
     float mx = -INFINITY, sum = 0.f;
-    for (int e = 0; e < n_all; ++e) mx = fmaxf(mx, z[e]);
-    for (int e = 0; e < n_all; ++e) { z[e] = expf(z[e] - mx); sum += z[e]; }
-    for (int e = 0; e < n_all; ++e) { z[e] = z[e] / sum; c[e] = z[e] + a.correction[e]; }
+    if (a.score_fn == 1) {
+      for (int e = 0; e < n_all; ++e) z[e] = 1.0f / (1.0f + expf(-z[e]));
+    } else {
+      for (int e = 0; e < n_all; ++e) mx = fmaxf(mx, z[e]);
+      for (int e = 0; e < n_all; ++e) { z[e] = expf(z[e] - mx); sum += z[e]; }
+      for (int e = 0; e < n_all; ++e) z[e] = z[e] / sum;
+    }
+    for (int e = 0; e < n_all; ++e) c[e] = z[e] + (a.correction ? a.correction[e] : 0.f);
     if (a.n_groups > 1 && a.keep_groups < a.n_groups) {
       const int per = n_all / a.n_groups;
       // drop the groups that are not among the best: n_groups - keep_groups times the worst
@@ -232,9 +247,10 @@ __global__ void __launch_bounds__(256) moe_up_kernel(const MoeArgs a) {
     const int row = ty * 4 + r;
     if (row >= n_rows) continue;
     float g = accg[r], u = accu[r];
+    if (a.weigh_input) { const float w = a.wts[a.perm[first + row]]; g *= w; u *= w; }
     g = fminf(g, a.limit);
     u = fminf(fmaxf(u, -a.limit), a.limit);
-    const float y = g / (1.0f + expf(-a.slope * g)) * (u + 1.0f);
+    const float y = g / (1.0f + expf(-a.slope * g)) * (u + a.up_offset);
     ((T*)a.act)[(size_t)(first + row) * F + f0 + tx] = from_f32<T>(y);
   }
 }
@@ -281,7 +297,7 @@ __global__ void __launch_bounds__(256) moe_down_kernel(const MoeArgs a) {
     const int row = ty * 4 + r;
     if (row >= n_rows) continue;
     const int p = pair[row], t = p / a.top, j = p % a.top;
-    a.out[((size_t)j * a.T + t) * W + n0 + tx] = a.wts[p] * acc[r];
+    a.out[((size_t)j * a.T + t) * W + n0 + tx] = (a.weigh_input ? 1.0f : a.wts[p]) * acc[r];
   }
 }
 
@@ -427,22 +443,23 @@ __global__ void __launch_bounds__(128) moe_tc_kernel(const MoeArgs a) {
       if (row >= n_rows) continue;
       if (UP) {
         bf16* dst = (bf16*)a.act + (size_t)(first + row) * N;
+        const float wi = a.weigh_input ? a.wts[a.perm[first + row]] : 1.0f;
 #pragma unroll
         for (int j = 0; j < NJ; ++j) {
           const int col = n0 + col_w + j * 8 + t * 2;
           float y[2];
 #pragma unroll
           for (int x = 0; x < 2; ++x) {
-            const float gt = fminf(acc[0][m][j][half * 2 + x], a.limit);
-            const float up = fminf(fmaxf(acc[NB - 1][m][j][half * 2 + x], -a.limit), a.limit);
-            y[x] = gt / (1.0f + expf(-a.slope * gt)) * (up + 1.0f);
+            const float gt = fminf(wi * acc[0][m][j][half * 2 + x], a.limit);
+            const float up = fminf(fmaxf(wi * acc[NB - 1][m][j][half * 2 + x], -a.limit), a.limit);
+            y[x] = gt / (1.0f + expf(-a.slope * gt)) * (up + a.up_offset);
           }
           if (col + 1 < N) *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16(y[0], y[1]);
           else if (col < N) dst[col] = from_f32<bf16>(y[0]);
         }
       } else {
         const int p = a.perm[first + row], tok = p / a.top, jc = p % a.top;
-        const float w = a.wts[p];
+        const float w = a.weigh_input ? 1.0f : a.wts[p];
         float* dst = a.out + ((size_t)jc * a.T + tok) * N;
 #pragma unroll
         for (int j = 0; j < NJ; ++j) {
@@ -474,7 +491,8 @@ static int moe_check(const MoeArgs& a) {
   const int n_all = a.E + a.n_identity;
   if (n_all % a.n_groups || a.top > n_all) return GB_ERR_BAD_ARG;
   if (n_all > MOE_MAX_OUTPUTS) return GB_ERR_UNSUPPORTED;
-  if (!a.x || !a.router_w || !a.correction || !a.w_gate || !a.w_up || !a.w_down || !a.ids || !a.wts ||
+  if (a.score_fn < 0 || a.score_fn > 1) return GB_ERR_BAD_ARG;
+  if (!a.x || !a.router_w || !a.w_gate || !a.w_up || !a.w_down || !a.ids || !a.wts ||
       !a.rank || !a.counts || !a.offsets || !a.perm || !a.act || !a.out)
     return GB_ERR_BAD_ARG;
   return 0;

@@ -1,0 +1,214 @@
+// Retention: linear attention with a fixed decay per head and neither softmax nor
+// denominator.  Per head, with q, k [dk] and v [dv] of a token,
+//
+//   S <- decay_h S + k v^T          (S [dk, dv], 32-bit, zero when the sequence starts)
+//   o  = S^T q
+//   y  = o / sqrt(mean(o^2) + eps) * silu(gate)
+//
+// q and k are rotated first: of every head's first `rot_dim` elements, element i
+// and element i + rot_dim/2 turn by pos * inv_freq[i]; k is then multiplied by
+// `k_scale`.  Everything here is 32-bit: the input is the 32-bit sums of the
+// mixer's one projection (columns q [H dk] | k [H dk] | v [H dv] | gate [H dv]),
+// and only y is rounded to the activation type.
+//
+// Three kernels.  `rotate` writes the turned q and scaled k of every row.  `scan`
+// walks a sequence's rows in order: a block owns one (sequence, head) and RT_COLS
+// columns of S; a column's dk elements live in the registers of eight lanes, the
+// rows' q, k and v are staged in shared memory RT_STAGE rows at a time, and the
+// eight partial read-outs of a column meet by shuffles.  The state is read once
+// and written once per step, for sequences whose slot is not negative (padding
+// rows read zeros and store nothing).  `finish` normalises a head's read-out and
+// applies the gate.
+#include "common.cuh"
+
+struct RetentionArgs {
+  const float* proj;      // [T, 2 H dk + 2 H dv]
+  const float* decay;     // [H]
+  const float* inv_freq;  // [rot_dim / 2]
+  const int* token_pos;   // [T]
+  const int* cu_q;        // [n_seqs + 1]
+  const int* slots;       // [n_seqs]
+  float* state;           // [slots, state_stride], a sequence's H matrices [dk, dv]
+  long long state_stride;
+  float* qk;              // [T, 2, H, dk] scratch: turned q, turned and scaled k
+  float* o;               // [T, H, dv] scratch: the read-outs
+  void* y;                // [T, H dv]
+  int n_tokens, n_seqs, H, dk, dv, rot_dim;
+  float k_scale, norm_eps;
+};
+
+#define RT_LANES 8      // lanes that share a column of the state
+#define RT_COLS 16      // columns a block owns
+#define RT_STAGE 16     // rows staged at a time
+
+__global__ void __launch_bounds__(256) retention_rotate_kernel(const RetentionArgs a) {
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int H = a.H, dk = a.dk, half = a.rot_dim / 2;
+  const int C = 2 * H * dk + 2 * H * a.dv;
+  const float* row = a.proj + (size_t)t * C;
+  float* out = a.qk + (size_t)t * 2 * H * dk;
+  const float pos = (float)a.token_pos[t];
+  // one thread per (q or k, head, element below dk - half): an element outside the
+  // rotated part passes, a rotated pair is written by the thread of its first element
+  for (int i = threadIdx.x; i < 2 * H * dk; i += blockDim.x) {
+    const int e = i % dk;
+    const float mul = i >= H * dk ? a.k_scale : 1.0f;
+    if (e >= a.rot_dim) { out[i] = row[i] * mul; continue; }
+    if (e >= half) continue;
+    float s, c;
+    sincosf(pos * a.inv_freq[e], &s, &c);
+    const float u = row[i], v = row[i + half];
+    out[i] = (u * c - v * s) * mul;
+    out[i + half] = (v * c + u * s) * mul;
+  }
+  pdl_launch_dependents_if_large();
+}
+
+// Row r of a lane's share of a column is element rt_row(lane, r) of the head: runs of four
+// neighbours per lane where a lane has a multiple of four (16-byte shared-memory reads
+// that the eight lanes of a column make side by side), else every eighth element.
+template <int KPL>
+__device__ __forceinline__ int rt_row(int lane, int r) {
+  return (KPL % 4 == 0) ? (r >> 2) * 32 + lane * 4 + (r & 3) : r * RT_LANES + lane;
+}
+
+template <int KPL>
+__global__ void __launch_bounds__(RT_COLS* RT_LANES) retention_scan_kernel(const RetentionArgs a) {
+  constexpr int DKP = KPL * RT_LANES;            // dk rounded up; the rest is zeros
+  __shared__ __align__(16) float qs[RT_STAGE][DKP];
+  __shared__ __align__(16) float ks[RT_STAGE][DKP];
+  __shared__ float vs[RT_STAGE][RT_COLS];
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  const int h = blockIdx.x, seq = blockIdx.y, c0 = blockIdx.z * RT_COLS;
+  const int H = a.H, dk = a.dk, dv = a.dv;
+  const int first = a.cu_q[seq], n = a.cu_q[seq + 1] - first;
+  if (n <= 0) return;
+  const int tid = threadIdx.x, lane = tid % RT_LANES, col = c0 + tid / RT_LANES;
+  const bool live = col < dv;
+  const int slot = a.slots[seq];
+  float* sp = slot >= 0 ? a.state + (size_t)slot * a.state_stride + (size_t)h * dk * dv : nullptr;
+  const float decay = a.decay[h];
+  float S[KPL];
+#pragma unroll
+  for (int r = 0; r < KPL; ++r) {
+    const int i = rt_row<KPL>(lane, r);
+    S[r] = (sp && live && i < dk) ? sp[(size_t)i * dv + col] : 0.f;
+  }
+  const int C = 2 * H * dk + 2 * H * dv;
+  for (int t0 = 0; t0 < n; t0 += RT_STAGE) {
+    const int nt = min(RT_STAGE, n - t0);
+    __syncthreads();
+    for (int i = tid; i < nt * DKP; i += blockDim.x) {
+      const int tt = i / DKP, e = i % DKP;
+      const float* src = a.qk + ((size_t)(first + t0 + tt) * 2 * H + h) * dk;
+      qs[tt][e] = e < dk ? src[e] : 0.f;
+      ks[tt][e] = e < dk ? src[(size_t)H * dk + e] : 0.f;
+    }
+    for (int i = tid; i < nt * RT_COLS; i += blockDim.x) {
+      const int tt = i / RT_COLS, c = c0 + i % RT_COLS;
+      vs[tt][i % RT_COLS] = c < dv ? a.proj[(size_t)(first + t0 + tt) * C + 2 * H * dk + h * dv + c] : 0.f;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float v = vs[tt][tid / RT_LANES];
+      float acc = 0.f;
+      if (KPL % 4 == 0) {
+#pragma unroll
+        for (int r = 0; r < KPL; r += 4) {
+          const float4 k4 = *reinterpret_cast<const float4*>(&ks[tt][rt_row<KPL>(lane, r)]);
+          const float4 q4 = *reinterpret_cast<const float4*>(&qs[tt][rt_row<KPL>(lane, r)]);
+          S[r] = fmaf(decay, S[r], k4.x * v);
+          S[r + 1] = fmaf(decay, S[r + 1], k4.y * v);
+          S[r + 2] = fmaf(decay, S[r + 2], k4.z * v);
+          S[r + 3] = fmaf(decay, S[r + 3], k4.w * v);
+          acc = fmaf(S[r], q4.x, acc);
+          acc = fmaf(S[r + 1], q4.y, acc);
+          acc = fmaf(S[r + 2], q4.z, acc);
+          acc = fmaf(S[r + 3], q4.w, acc);
+        }
+      } else {
+#pragma unroll
+        for (int r = 0; r < KPL; ++r) {
+          const int i = rt_row<KPL>(lane, r);
+          S[r] = fmaf(decay, S[r], ks[tt][i] * v);
+          acc = fmaf(S[r], qs[tt][i], acc);
+        }
+      }
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+      if (lane == 0 && live) a.o[((size_t)(first + t0 + tt) * H + h) * dv + col] = acc;
+    }
+  }
+  pdl_launch_dependents_if_large();
+  if (sp && live) {
+#pragma unroll
+    for (int r = 0; r < KPL; ++r) {
+      const int i = rt_row<KPL>(lane, r);
+      if (i < dk) sp[(size_t)i * dv + col] = S[r];
+    }
+  }
+}
+
+// y[t, h, :] = o / sqrt(mean(o^2) + eps) * silu(gate): one warp per (row, head)
+template <typename T>
+__global__ void __launch_bounds__(128) retention_finish_kernel(const RetentionArgs a) {
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= (long long)a.n_tokens * a.H) return;
+  const int t = (int)(w / a.H), h = (int)(w % a.H), dv = a.dv;
+  const int C = 2 * a.H * a.dk + 2 * a.H * dv;
+  const float* o = a.o + ((size_t)t * a.H + h) * dv;
+  const float* g = a.proj + (size_t)t * C + 2 * a.H * a.dk + a.H * dv + h * dv;
+  float ss = 0.f;
+  for (int i = lane; i < dv; i += 32) ss = fmaf(o[i], o[i], ss);
+  const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)dv + a.norm_eps);
+  pdl_launch_dependents_if_large();
+  T* y = (T*)a.y + ((size_t)t * a.H + h) * dv;
+  for (int i = lane; i < dv; i += 32) {
+    const float gv = g[i];
+    y[i] = from_f32<T>(o[i] * inv * (gv / (1.0f + expf(-gv))));
+  }
+}
+
+template <int KPL>
+static int retention_scan_launch(const RetentionArgs& a, cudaStream_t s) {
+  return gb_launch(retention_scan_kernel<KPL>, dim3(a.H, a.n_seqs, (a.dv + RT_COLS - 1) / RT_COLS),
+                   dim3(RT_COLS * RT_LANES), 0, s, a);
+}
+
+template <typename T>
+static int retention_forward(const RetentionArgs& a, cudaStream_t s) {
+  if (a.n_tokens < 0 || a.n_seqs < 0 || a.H <= 0 || a.dk <= 0 || a.dv <= 0 || a.rot_dim < 0 ||
+      a.rot_dim > a.dk || a.rot_dim % 2 || a.n_seqs > 65535)
+    return GB_ERR_BAD_ARG;
+  if (!a.proj || !a.decay || !a.token_pos || !a.cu_q || !a.slots || !a.state || !a.qk || !a.o ||
+      !a.y || (a.rot_dim && !a.inv_freq))
+    return GB_ERR_BAD_ARG;
+  if (a.dk > 256) return GB_ERR_UNSUPPORTED;
+  if (a.n_tokens == 0 || a.n_seqs == 0) return 0;
+  int e = gb_launch(retention_rotate_kernel, dim3(a.n_tokens), dim3(256), 0, s, a);
+  if (e) return e;
+  const int kpl = (a.dk + RT_LANES - 1) / RT_LANES;
+  if (kpl <= 1) e = retention_scan_launch<1>(a, s);
+  else if (kpl <= 2) e = retention_scan_launch<2>(a, s);
+  else if (kpl <= 4) e = retention_scan_launch<4>(a, s);
+  else if (kpl <= 8) e = retention_scan_launch<8>(a, s);
+  else if (kpl <= 16) e = retention_scan_launch<16>(a, s);
+  else e = retention_scan_launch<32>(a, s);
+  if (e) return e;
+  const long long warps = (long long)a.n_tokens * a.H;
+  return gb_launch(retention_finish_kernel<T>, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, s, a);
+}
+
+GB_EXPORT int gb_retention_forward_f32(const RetentionArgs* a, cudaStream_t s) {
+  return retention_forward<float>(*a, s);
+}
+GB_EXPORT int gb_retention_forward_bf16(const RetentionArgs* a, cudaStream_t s) {
+  return retention_forward<bf16>(*a, s);
+}

@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import ctypes
 import functools
+import math
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional, Tuple
 
@@ -242,6 +243,19 @@ def embed(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
     sfx = _suffix(table.dtype)
     _check(_fn("embed", f"gb_embed_{sfx}", "pppiiip")(
         table.data_ptr(), ids.data_ptr(), out.data_ptr(), ids.shape[0], H, V, _stream()), "embed")
+    return out
+
+
+@_profiled("embed_scaled", lambda out, table, ids, scale: (_nbytes(ids, out) + out.numel() * table.element_size(), 0))
+def embed_scaled(table: torch.Tensor, ids: torch.Tensor, scale: float) -> torch.Tensor:
+    """scale * table[ids[t]] as 32-bit rows [T, H] (the product is 32-bit whatever the table's type)."""
+    _need(table, "embedding table", ndim=2)
+    _need(ids, "token ids", torch.int32, 1)
+    V, H = table.shape
+    out = torch.empty((ids.shape[0], H), dtype=torch.float32, device=table.device)
+    _check(_fn("embed", f"gb_embed_scaled_{_suffix(table.dtype)}", "ppfpiiip")(
+        table.data_ptr(), ids.data_ptr(), float(scale), out.data_ptr(), ids.shape[0], H, V, _stream()),
+        "embed_scaled")
     return out
 
 
@@ -642,6 +656,54 @@ def gelu_tanh_mul(gate_up: torch.Tensor, interleave: int = 0) -> torch.Tensor:
     _check(_fn("elementwise", f"gb_gelu_tanh_mul_{_suffix(gate_up.dtype)}", "ppiiip")(
         gate_up.data_ptr(), out.data_ptr(), T, two_i // 2, int(interleave), _stream()), "gelu_tanh_mul")
     return out
+
+
+GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu": 2}
+
+
+@_profiled("relu_mul", _cost_io)
+def relu_mul(gate_up: torch.Tensor, interleave: int = 0) -> torch.Tensor:
+    """max(gate, 0) * up; the layout of ``gate_up`` is that of ``silu_mul``."""
+    _need(gate_up, "gate|up", ndim=2)
+    T, two_i = gate_up.shape
+    if two_i % 2 or (interleave and two_i % (2 * interleave)):
+        raise KernelError("gate|up must have an even number of columns (of whole groups)")
+    out = torch.empty((T, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    _check(_fn("elementwise", f"gb_relu_mul_{_suffix(gate_up.dtype)}", "ppiiip")(
+        gate_up.data_ptr(), out.data_ptr(), T, two_i // 2, int(interleave), _stream()), "relu_mul")
+    return out
+
+
+@_profiled("bias_gate_mul", _cost_io)
+def bias_gate_mul(gate_up: torch.Tensor, bias: torch.Tensor, activation: str, dtype: torch.dtype,
+                  interleave: int = 0) -> torch.Tensor:
+    """act(gate + bias_g) * (up + bias_u) on the 32-bit sums ``gate_up`` [T, 2 I] of a fused
+    gate|up product, rounded once to ``dtype``; ``bias`` [2 I] 32-bit in the layout of
+    ``gate_up`` (``interleave`` as in ``silu_mul``); ``activation`` silu, gelu_tanh or relu."""
+    _need(gate_up, "gate|up sums", torch.float32, 2)
+    _need(bias, "gate|up bias", torch.float32, 1)
+    T, two_i = gate_up.shape
+    if two_i % 2 or (interleave and two_i % (2 * interleave)) or bias.shape[0] != two_i:
+        raise KernelError("gate|up must have an even number of columns (of whole groups) and a bias for each")
+    if activation not in GATE_ACTIVATIONS:
+        raise KernelError(f"activation '{activation}': one of {list(GATE_ACTIVATIONS)}")
+    out = torch.empty((T, two_i // 2), dtype=dtype, device=gate_up.device)
+    _check(_fn("elementwise", f"gb_bias_gate_mul_{_suffix(dtype)}", "pppiiiip")(
+        gate_up.data_ptr(), bias.data_ptr(), out.data_ptr(), T, two_i // 2, int(interleave),
+        GATE_ACTIVATIONS[activation], _stream()), "bias_gate_mul")
+    return out
+
+
+@_profiled("add_bias", lambda out, x, bias: (2 * _nbytes(x), 0))
+def add_bias_(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """x[..., :] += bias in place on contiguous 32-bit rows."""
+    _need(x, "rows", torch.float32)
+    _need(bias, "bias", torch.float32, 1)
+    if x.shape[-1] != bias.shape[0] or not x.is_contiguous():
+        raise KernelError(f"rows of {x.shape[-1]} (contiguous) and a bias of {bias.shape[0]} do not fit")
+    _check(_fn("elementwise", "gb_add_bias_f32", "pplip")(
+        x.data_ptr(), bias.data_ptr(), x.numel() // x.shape[-1], x.shape[-1], _stream()), "add_bias")
+    return x
 
 
 @_profiled("relu_squared", _cost_io)
@@ -1419,13 +1481,227 @@ def delta_forward(proj: torch.Tensor, state: torch.Tensor, conv_w: torch.Tensor,
     return y
 
 
+# ---------------------------------------------------------------- retention
+class _RetentionArgs(ctypes.Structure):
+    _fields_ = [("proj", _P), ("decay", _P), ("inv_freq", _P), ("token_pos", _P), ("cu_q", _P),
+                ("slots", _P), ("state", _P), ("state_stride", _L), ("qk", _P), ("o", _P), ("y", _P),
+                ("n_tokens", _I), ("n_seqs", _I), ("H", _I), ("dk", _I), ("dv", _I), ("rot_dim", _I),
+                ("k_scale", _F), ("norm_eps", _F)]
+
+
+def _cost_retention(out, proj, state, *a, H, dk, dv, **k):
+    T = proj.shape[0]
+    n_seqs = k["slots"].shape[0]
+    return (_nbytes(proj, out) + T * (4 * H * dk + 2 * H * dv) * 4 + 2 * n_seqs * H * dk * dv * 4,
+            4.0 * T * H * dk * dv)
+
+
+@_profiled("retention_forward", _cost_retention)
+def retention_forward(proj: torch.Tensor, state: torch.Tensor, decay: torch.Tensor,
+                      inv_freq: Optional[torch.Tensor], *, H: int, dk: int, dv: int, rot_dim: int,
+                      k_scale: float, norm_eps: float, token_pos, cu_q, slots,
+                      dtype: torch.dtype) -> torch.Tensor:
+    """Retention on the rows of a step.  ``proj`` [T, 2 H dk + 2 H dv] 32-bit: the columns
+    q | k | v | gate of the mixer's one projection; ``state`` [slots, H dk dv] 32-bit, updated
+    in place for the sequences whose slot is not negative; ``decay`` [H] 32-bit; ``inv_freq``
+    [rot_dim / 2] the rotation's frequencies (element i of a head goes with element
+    i + rot_dim / 2).  Returns y [T, H dv] in ``dtype``: every head's read-out S^T q,
+    divided by its root mean square over dv (``norm_eps`` under the root), times silu(gate)."""
+    _need(proj, "projection", torch.float32, 2)
+    _need(state, "state", torch.float32, 2)
+    _need(decay, "decay", torch.float32, 1)
+    T = proj.shape[0]
+    if proj.shape[1] != 2 * H * dk + 2 * H * dv:
+        raise KernelError(f"the projection has {proj.shape[1]} columns, expected {2 * H * dk + 2 * H * dv}")
+    if state.shape[1] != H * dk * dv or decay.shape[0] != H:
+        raise KernelError(f"a sequence's state has {state.shape[1]} floats, expected {H * dk * dv}, "
+                          f"and there is a decay for each of {H} heads")
+    if rot_dim:
+        _need(inv_freq, "inv_freq", torch.float32, 1)
+        if inv_freq.shape[0] * 2 != rot_dim or rot_dim > dk:
+            raise KernelError("inv_freq must hold rot_dim / 2 entries, rot_dim at most the head's size")
+    for t, nm in ((token_pos, "token_pos"), (cu_q, "cu_q"), (slots, "slots")):
+        _need(t, nm, torch.int32, 1)
+    n_seqs = slots.shape[0]
+    if token_pos.shape[0] != T or cu_q.shape[0] != n_seqs + 1:
+        raise KernelError("token_pos, cu_q and slots do not describe the step's rows")
+    dev = proj.device
+    qk = torch.empty((T, 2, H, dk), dtype=torch.float32, device=dev)
+    o = torch.empty((T, H, dv), dtype=torch.float32, device=dev)
+    y = torch.empty((T, H * dv), dtype=dtype, device=dev)
+    a = _RetentionArgs()
+    a.proj, a.decay, a.inv_freq = proj.data_ptr(), decay.data_ptr(), _ptr(inv_freq)
+    a.token_pos, a.cu_q, a.slots = token_pos.data_ptr(), cu_q.data_ptr(), slots.data_ptr()
+    a.state, a.state_stride = state.data_ptr(), state.stride(0)
+    a.qk, a.o, a.y = qk.data_ptr(), o.data_ptr(), y.data_ptr()
+    a.n_tokens, a.n_seqs, a.H, a.dk, a.dv, a.rot_dim = T, n_seqs, H, dk, dv, int(rot_dim)
+    a.k_scale, a.norm_eps = float(k_scale), float(norm_eps)
+    _check(_fn("retention", f"gb_retention_forward_{_suffix(dtype)}", "pp")(ctypes.addressof(a), _stream()),
+           "retention_forward", 3)
+    return y
+
+
+# ---------------------------------------------------------------- gated linear recurrence
+class _RglruArgs(ctypes.Structure):
+    _fields_ = [("proj", _P), ("bias", _P), ("conv_w", _P), ("conv_b", _P), ("wa_t", _P), ("ba", _P),
+                ("wi_t", _P), ("bi", _P), ("lam", _P), ("token_seq", _P), ("cu_q", _P), ("slots", _P),
+                ("state", _P), ("state_stride", _L), ("u", _P), ("ab", _P), ("out", _P),
+                ("n_tokens", _I), ("n_seqs", _I), ("C", _I), ("blocks", _I), ("taps", _I),
+                ("factor", _F)]
+
+
+def _cost_rglru(out, proj, state, *a, **k):
+    T, C2 = proj.shape
+    C = C2 // 2
+    bw = C // k["blocks"]
+    return (_nbytes(proj, out) + T * C * 4 * 6, 4.0 * T * C * bw)
+
+
+@_profiled("rglru_forward", _cost_rglru)
+def rglru_forward(proj: torch.Tensor, state: torch.Tensor, bias: torch.Tensor, conv_w: torch.Tensor,
+                  conv_b: torch.Tensor, wa_t: torch.Tensor, ba: torch.Tensor, wi_t: torch.Tensor,
+                  bi: torch.Tensor, lam: torch.Tensor, *, blocks: int, taps: int, factor: float,
+                  token_seq, cu_q, slots, dtype: torch.dtype) -> torch.Tensor:
+    """The gated linear recurrence on the rows of a step.  ``proj`` [T, 2 C] 32-bit: the
+    columns y | x of the mixer's projection, ``bias`` [2 C] their biases; ``conv_w`` [C, taps]
+    and ``conv_b`` [C] the convolution over x; ``wa_t``, ``wi_t`` [blocks, C / blocks, C / blocks]
+    the gates' matrices per part of the channels, each stored [in, out], with biases ``ba``,
+    ``bi`` [C]; ``lam`` [C]; the decay is exp(-factor * r * softplus(lam)).  ``state``
+    [slots, taps * C] 32-bit: the last taps - 1 inputs of the convolution, then S; updated
+    in place for sequences whose slot is not negative.  Returns S * gelu_tanh(y) [T, C] in ``dtype``."""
+    _need(proj, "projection", torch.float32, 2)
+    _need(state, "state", torch.float32, 2)
+    T, C2 = proj.shape
+    C = C2 // 2
+    if C2 % 2 or C % blocks:
+        raise KernelError(f"{C2} columns are not two branches of {blocks} equal parts")
+    bw = C // blocks
+    for t, nm, shape in ((bias, "projection biases", (2 * C,)), (conv_w, "convolution weights", (C, taps)),
+                         (conv_b, "convolution bias", (C,)), (wa_t, "decay gate", (blocks, bw, bw)),
+                         (wi_t, "input gate", (blocks, bw, bw)), (ba, "decay gate bias", (C,)),
+                         (bi, "input gate bias", (C,)), (lam, "lam", (C,))):
+        _need(t, nm, torch.float32)
+        if tuple(t.shape) != shape:
+            raise KernelError(f"{nm} are {tuple(t.shape)}, expected {shape}")
+    if state.shape[1] != taps * C:
+        raise KernelError(f"a sequence's state has {state.shape[1]} floats, expected {taps * C}")
+    for t, nm in ((token_seq, "token_seq"), (cu_q, "cu_q"), (slots, "slots")):
+        _need(t, nm, torch.int32, 1)
+    n_seqs = slots.shape[0]
+    if token_seq.shape[0] != T or cu_q.shape[0] != n_seqs + 1:
+        raise KernelError("token_seq, cu_q and slots do not describe the step's rows")
+    dev = proj.device
+    u = torch.empty((T, C), dtype=torch.float32, device=dev)
+    ab = torch.empty((T, 2, C), dtype=torch.float32, device=dev)
+    out = torch.empty((T, C), dtype=dtype, device=dev)
+    a = _RglruArgs()
+    a.proj, a.bias, a.conv_w, a.conv_b = proj.data_ptr(), bias.data_ptr(), conv_w.data_ptr(), conv_b.data_ptr()
+    a.wa_t, a.ba, a.wi_t, a.bi, a.lam = wa_t.data_ptr(), ba.data_ptr(), wi_t.data_ptr(), bi.data_ptr(), lam.data_ptr()
+    a.token_seq, a.cu_q, a.slots = token_seq.data_ptr(), cu_q.data_ptr(), slots.data_ptr()
+    a.state, a.state_stride = state.data_ptr(), state.stride(0)
+    a.u, a.ab, a.out = u.data_ptr(), ab.data_ptr(), out.data_ptr()
+    a.n_tokens, a.n_seqs, a.C, a.blocks, a.taps, a.factor = T, n_seqs, C, int(blocks), int(taps), float(factor)
+    _check(_fn("rglru", f"gb_rglru_forward_{_suffix(dtype)}", "pp")(ctypes.addressof(a), _stream()),
+           "rglru_forward", 3)
+    return out
+
+
+# ---------------------------------------------------------------- latent attention
+class _LatentArgs(ctypes.Structure):
+    _fields_ = [("proj", _P), ("norm_w", _P), ("inv_freq", _P), ("token_seq", _P), ("token_pos", _P),
+                ("slots", _P), ("block_table", _P), ("pages", _P), ("q_plain", _P), ("q_full", _P),
+                ("n_tokens", _I), ("H", _I), ("dn", _I), ("dr", _I), ("R", _I), ("dv", _I), ("Ds", _I),
+                ("max_pages", _I), ("page", _I), ("eps", _F)]
+
+
+@_profiled("latent_prepare", lambda out, proj, *a, **k: (_nbytes(proj) + _nbytes(*out), 0))
+def latent_prepare(proj: torch.Tensor, norm_w: torch.Tensor, inv_freq: Optional[torch.Tensor], *,
+                   H: int, dn: int, dr: int, R: int, dv: int, eps: float, token_seq, token_pos,
+                   slots, block_table, pages, page: int, dtype: torch.dtype):
+    """What latent attention does between its projection and its attention.  ``proj``
+    [T, H (dn + dr) + R + dr + H dv] 32-bit: queries (per head dn plain, dr rotated
+    elements) | the down projection | the gate.  Stores the row [c | k_rot | zeros] of
+    every token whose slot is not negative in ``pages`` [n, 1, page, Ds] (c: the first R
+    numbers of the down projection, RMS-normalised times ``norm_w``; k_rot: its last dr,
+    rotated: element 2i with element 2i + 1 by position * inv_freq[i]).  Returns
+    (q_plain [T, H, dn], q_full [T, H, Ds]) in ``dtype``; of q_full the columns from R on
+    are written (the rotated query part, then zeros), the first R are left to the caller."""
+    _need(proj, "projection", torch.float32, 2)
+    _need(norm_w, "latent norm weight", torch.float32, 1)
+    T = proj.shape[0]
+    _need(pages, "latent pages", dtype, 4)
+    Ds = pages.shape[-1]
+    if proj.shape[1] != H * (dn + dr) + R + dr + H * dv or norm_w.shape[0] != R:
+        raise KernelError(f"the projection has {proj.shape[1]} columns, expected "
+                          f"{H * (dn + dr) + R + dr + H * dv}; the norm weight {norm_w.shape[0]} for {R}")
+    if tuple(pages.shape[1:]) != (1, page, Ds) or Ds < R + dr:
+        raise KernelError(f"pages are {tuple(pages.shape)}, expected [*, 1, {page}, >= {R + dr}]")
+    if dr:
+        _need(inv_freq, "inv_freq", torch.float32, 1)
+        if inv_freq.shape[0] * 2 != dr:
+            raise KernelError("inv_freq must hold dr / 2 entries")
+    for t, nm in ((token_seq, "token_seq"), (token_pos, "token_pos"), (slots, "slots")):
+        _need(t, nm, torch.int32, 1)
+    _need(block_table, "block table", torch.int32, 2)
+    q_plain = torch.empty((T, H, dn), dtype=dtype, device=proj.device)
+    q_full = torch.empty((T, H, Ds), dtype=dtype, device=proj.device)
+    a = _LatentArgs()
+    a.proj, a.norm_w, a.inv_freq = proj.data_ptr(), norm_w.data_ptr(), _ptr(inv_freq)
+    a.token_seq, a.token_pos, a.slots = token_seq.data_ptr(), token_pos.data_ptr(), slots.data_ptr()
+    a.block_table, a.pages = block_table.data_ptr(), pages.data_ptr()
+    a.q_plain, a.q_full = q_plain.data_ptr(), q_full.data_ptr()
+    a.n_tokens, a.H, a.dn, a.dr, a.R, a.dv, a.Ds = T, H, dn, dr, R, dv, Ds
+    a.max_pages, a.page, a.eps = block_table.shape[1], int(page), float(eps)
+    _check(_fn("latent", f"gb_latent_prepare_{_suffix(dtype)}", "pp")(ctypes.addressof(a), _stream()),
+           "latent_prepare")
+    return q_plain, q_full
+
+
+class _HeadsMmArgs(ctypes.Structure):
+    _fields_ = [("x", _P), ("w", _P), ("out", _P), ("g", _P), ("T", _I), ("H", _I), ("K", _I),
+                ("N", _I), ("ldx", _I), ("ldo", _I), ("ldg", _I)]
+
+
+@_profiled("heads_mm", lambda out, x, w, *a, **k: (_nbytes(x, w) + x.shape[0] * w.shape[0] * w.shape[1] * x.element_size(),
+                                                    2.0 * x.shape[0] * w.shape[0] * w.shape[1] * w.shape[2]))
+def heads_mm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *,
+             gate: Optional[torch.Tensor] = None, gate_col: int = 0) -> torch.Tensor:
+    """A product per head: out[t, h, :N] = w[h] x[t, h, :K] with x [T, H, ldx >= K], w [H, N, K]
+    and out [T, H, ldo >= N] (made [T, H, N] when not given; columns from N on are left as
+    they are).  ``gate`` [T, ld] 32-bit: the result is multiplied, on its 32-bit sums, by
+    sigmoid(gate[t, gate_col + h N + n])."""
+    _need(x, "rows per head", ndim=3)
+    _need(w, "weights per head", x.dtype, 3)
+    T, H, ldx = x.shape
+    Hw, N, K = w.shape
+    if Hw != H or K > ldx or not x.is_contiguous() or not w.is_contiguous():
+        raise KernelError(f"rows {tuple(x.shape)} and weights {tuple(w.shape)} do not fit together")
+    if out is None:
+        out = torch.empty((T, H, N), dtype=x.dtype, device=x.device)
+    _need(out, "result", x.dtype, 3)
+    if out.shape[0] != T or out.shape[1] != H or out.shape[2] < N or not out.is_contiguous():
+        raise KernelError(f"the result is {tuple(out.shape)}, expected [{T}, {H}, >= {N}]")
+    a = _HeadsMmArgs()
+    a.x, a.w, a.out = x.data_ptr(), w.data_ptr(), out.data_ptr()
+    a.T, a.H, a.K, a.N, a.ldx, a.ldo = T, H, K, N, ldx, out.shape[2]
+    if gate is not None:
+        _need(gate, "gate", torch.float32, 2)
+        if gate.shape[0] != T or gate_col + H * N > gate.shape[1] or gate.stride(1) != 1:
+            raise KernelError("the gate's rows do not hold the heads' columns")
+        a.g, a.ldg = gate.data_ptr() + 4 * int(gate_col), gate.stride(0)
+    _check(_fn("latent", f"gb_heads_mm_{_suffix(x.dtype)}", "pp")(ctypes.addressof(a), _stream()),
+           "heads_mm")
+    return out
+
+
 # ---------------------------------------------------------------- routed experts
 class _MoeArgs(ctypes.Structure):
     _fields_ = [("x", _P), ("router_w", _P), ("correction", _P), ("w_gate", _P), ("w_up", _P),
                 ("w_down", _P), ("ids", _P), ("wts", _P), ("rank", _P), ("counts", _P),
                 ("offsets", _P), ("perm", _P), ("act", _P), ("out", _P), ("T", _I), ("W", _I),
                 ("F", _I), ("E", _I), ("n_identity", _I), ("top", _I), ("n_groups", _I),
-                ("keep_groups", _I), ("limit", _F), ("slope", _F)]
+                ("keep_groups", _I), ("limit", _F), ("slope", _F), ("score_fn", _I),
+                ("weigh_input", _I), ("up_offset", _F)]
 
 
 _MOE_COUNTS = {}
@@ -1439,27 +1715,35 @@ def _cost_moe(out, x, router_w, correction, w_gate, w_up, w_down, *, top, **k):
 
 
 @_profiled("moe_forward", _cost_moe)
-def moe_forward(x: torch.Tensor, router_w: torch.Tensor, correction: torch.Tensor,
+def moe_forward(x: torch.Tensor, router_w: torch.Tensor, correction: Optional[torch.Tensor],
                 w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, *, top: int,
-                n_identity: int, n_groups: int, keep_groups: int, limit: float, slope: float,
-                want_choice: bool = False):
+                n_identity: int = 0, n_groups: int = 1, keep_groups: int = 1,
+                limit: float = math.inf, slope: float = 1.0, score_fn: str = "softmax",
+                weigh_input: bool = False, up_offset: float = 1.0, want_choice: bool = False):
     """A feed-forward of routed experts on rows x [T, W] -> 32-bit partial sums
     [top, T, W], choice j of every token in [j], already weighted; their sum is the
     feed-forward's output.  ``router_w`` [E + n_identity, W] and ``correction`` are
     32-bit; the experts' weights [E, F, W], [E, F, W], [E, W, F] have the type of x.
     The last ``n_identity`` router outputs stand for experts that return their input.
+    ``score_fn`` "sigmoid" scores every output by itself instead of by the softmax;
+    ``correction`` may be None; ``weigh_input`` multiplies the expert's input, not its
+    result, by the weight; an expert is Wd (g sigmoid(slope g) (u + up_offset)) with g
+    and u clamped at ``limit``.
     With ``want_choice`` also returns (ids [T, top] int32, weights [T, top])."""
     _need(x, "activations", ndim=2)
     T, W = x.shape
     _need(router_w, "router weight", torch.float32, 2)
-    _need(correction, "score correction", torch.float32, 1)
+    if correction is not None:
+        _need(correction, "score correction", torch.float32, 1)
+    if score_fn not in ("softmax", "sigmoid"):
+        raise KernelError(f"score function '{score_fn}': softmax or sigmoid")
     for t, nm in ((w_gate, "gate weights"), (w_up, "up weights"), (w_down, "down weights")):
         _need(t, nm, x.dtype, 3)
     E, F = w_gate.shape[0], w_gate.shape[1]
     n_all = E + n_identity
     if tuple(w_gate.shape) != (E, F, W) or tuple(w_up.shape) != (E, F, W) or \
             tuple(w_down.shape) != (E, W, F) or tuple(router_w.shape) != (n_all, W) or \
-            correction.shape[0] != n_all:
+            (correction is not None and correction.shape[0] != n_all):
         raise KernelError("the experts' weights, the router and the correction do not fit together")
     dev = x.device
     ids = torch.empty((T, top), dtype=torch.int32, device=dev)
@@ -1474,12 +1758,13 @@ def moe_forward(x: torch.Tensor, router_w: torch.Tensor, correction: torch.Tenso
     if counts is None:
         counts = _MOE_COUNTS[key] = torch.zeros((E + 1,), dtype=torch.int32, device=dev)
     a = _MoeArgs()
-    a.x, a.router_w, a.correction = x.data_ptr(), router_w.data_ptr(), correction.data_ptr()
+    a.x, a.router_w, a.correction = x.data_ptr(), router_w.data_ptr(), _ptr(correction)
     a.w_gate, a.w_up, a.w_down = w_gate.data_ptr(), w_up.data_ptr(), w_down.data_ptr()
     a.ids, a.wts, a.rank, a.counts = ids.data_ptr(), wts.data_ptr(), rank.data_ptr(), counts.data_ptr()
     a.offsets, a.perm, a.act, a.out = offsets.data_ptr(), perm.data_ptr(), act.data_ptr(), out.data_ptr()
     a.T, a.W, a.F, a.E, a.n_identity, a.top = T, W, F, E, int(n_identity), int(top)
     a.n_groups, a.keep_groups, a.limit, a.slope = int(n_groups), int(keep_groups), float(limit), float(slope)
+    a.score_fn, a.weigh_input, a.up_offset = int(score_fn == "sigmoid"), int(weigh_input), float(up_offset)
     _check(_fn("moe", f"gb_moe_forward_{_suffix(x.dtype)}", "pp")(ctypes.addressof(a), _stream()),
            "moe_forward", 3)
     return (out, ids, wts) if want_choice else out

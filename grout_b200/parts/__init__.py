@@ -4,8 +4,8 @@ from .block import Block, PostNormBlock, PreNormBlock, SandwichBlock
 from .feedforward import FeedForward, GatedMLP, ReluSquaredMLP, RoutedExperts, SwiGLU
 from .io import Embedding, Head, LinearHead, TokenEmbedding, TokenPositionalEmbedding
 from .linear import Linear
-from .mixer import GQAAttention, Mixer
-from .recurrent import GatedDelta
+from .mixer import GQAAttention, LatentAttention, Mixer
+from .recurrent import GatedDelta, GatedLinearRecurrence, Retention
 from .norm import Contribution, LayerNorm, Norm, RMSNorm, residual_add, stream_add
 from .plan import LayerPlan, ModelPlan, ScheduleEntry
 from .position import NoPosition, PositionEncoding, RotaryHalfSplit, RotaryTable

@@ -30,23 +30,27 @@ class Block(Part):
 
 @register_part("block", "prenorm")
 class PreNormBlock(Block):
-    """x += mixer(norm1(x)); x += feedforward(norm2(x)) (src/training.rs:303-349)."""
+    """x += mixer(norm1(x)); x += feedforward(norm2(x)) (src/training.rs:303-349).
+    The second line is absent when the layer has no feed-forward (neither ``norm2``
+    nor ``feedforward`` is given)."""
 
     roles = ("norm1", "mixer", "norm2", "feedforward")
 
-    def __init__(self, ctx: BuildContext, norm1: PartSpec, mixer: PartSpec, norm2: PartSpec,
-                 feedforward: PartSpec):
+    def __init__(self, ctx: BuildContext, norm1: PartSpec, mixer: PartSpec,
+                 norm2: Optional[PartSpec] = None, feedforward: Optional[PartSpec] = None):
         super().__init__(ctx)
+        if (norm2 is None) != (feedforward is None):
+            raise ValueError("a feed-forward comes with its norm, or neither is given")
         self.norm1 = build_part("norm", norm1, ctx)
         self.mixer = build_part("mixer", mixer, ctx)
-        self.norm2 = build_part("norm", norm2, ctx)
-        self.feedforward = build_part("feedforward", feedforward, ctx)
+        self.norm2 = build_part("norm", norm2, ctx) if norm2 else None
+        self.feedforward = build_part("feedforward", feedforward, ctx) if feedforward else None
 
     def children(self):
-        return (self.norm1, self.mixer, self.norm2, self.feedforward)
+        return tuple(self.named_parts().values())
 
     def named_parts(self) -> Dict[str, Part]:
-        return {r: getattr(self, r) for r in self.roles}
+        return {r: getattr(self, r) for r in self.roles if getattr(self, r) is not None}
 
     def cache_spec(self):
         return self.mixer.cache_spec()
@@ -57,6 +61,8 @@ class PreNormBlock(Block):
     def forward(self, res, pending, step, cache):
         res, n = self.norm1.add_norm(res, pending)
         a = self.mixer.forward(n, step, cache)
+        if self.feedforward is None:
+            return res, a
         res, m = self.norm2.add_norm(res, a)
         return res, self.feedforward.forward(m, step)
 

@@ -5,6 +5,9 @@ routes inside ``forward``; the rows' packing is the step's and does not change.
 """
 from __future__ import annotations
 
+import math
+from typing import Optional
+
 import torch
 
 from ..kernels import ops
@@ -95,29 +98,40 @@ class ReluSquaredMLP(FeedForward):
 
 @register_part("feedforward", "gated_mlp")
 class GatedMLP(FeedForward):
-    """d = (act(x Wg^T) * (x Wu^T)) Wd^T, no biases, with ``activation`` "silu" or
-    "gelu_tanh" (0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))).  Gate and up are
+    """d = (act(x Wg^T) * (x Wu^T)) Wd^T with ``activation`` "silu", "gelu_tanh"
+    (0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))) or "relu".  Gate and up are
     one product; the activation and the multiplication are taken in 32-bit on its
-    result.  ``names``: the local names of the three tensors (keys gate, up, down)."""
+    result.  With ``bias`` each of the three projections has a bias,
+    d = (act(x Wg^T + bg) * (x Wu^T + bu)) Wd^T + bd: the biases are added to the
+    products' 32-bit sums, and the result leaves as 32-bit sums for the next norm to
+    add.  ``names``: the tensors' local names (keys gate, up, down and, with biases,
+    gate_bias, up_bias, down_bias)."""
 
-    ACTIVATIONS = ("silu", "gelu_tanh")
+    ACTIVATIONS = ("silu", "gelu_tanh", "relu")
 
     def __init__(self, ctx: BuildContext, hidden: int, intermediate: int,
-                 activation: str = "silu", names=None):
+                 activation: str = "silu", names=None, bias: bool = False):
         super().__init__(ctx)
         if activation not in self.ACTIVATIONS:
             raise ValueError(f"activation '{activation}': one of {list(self.ACTIVATIONS)}")
         self.hidden, self.intermediate, self.activation = int(hidden), int(intermediate), activation
+        self.has_bias = bool(bias)
         self.names = dict({"gate": "gate_proj.weight", "up": "up_proj.weight",
-                           "down": "down_proj.weight"}, **(names or {}))
-        self.gate_up = self.down = None
+                           "down": "down_proj.weight", "gate_bias": "gate_proj.bias",
+                           "up_bias": "up_proj.bias", "down_bias": "down_proj.bias"}, **(names or {}))
+        self.gate_up = self.down = self.gate_up_bias = self.down_bias = None
         self.interleave = 0
 
     def param_specs(self):
         nm = self.names
-        return {nm["gate"]: ParamSpec((self.intermediate, self.hidden)),
-                nm["up"]: ParamSpec((self.intermediate, self.hidden)),
-                nm["down"]: ParamSpec((self.hidden, self.intermediate))}
+        specs = {nm["gate"]: ParamSpec((self.intermediate, self.hidden)),
+                 nm["up"]: ParamSpec((self.intermediate, self.hidden)),
+                 nm["down"]: ParamSpec((self.hidden, self.intermediate))}
+        if self.has_bias:
+            specs.update({nm["gate_bias"]: ParamSpec((self.intermediate,), "offset"),
+                          nm["up_bias"]: ParamSpec((self.intermediate,), "offset"),
+                          nm["down_bias"]: ParamSpec((self.hidden,), "offset")})
+        return specs
 
     def load(self, params):
         g, u = params[self.names["gate"]], params[self.names["up"]]
@@ -134,6 +148,15 @@ class GatedMLP(FeedForward):
         else:
             self.gate_up = Linear(torch.cat([g, u], dim=0), self.ctx.products)
         self.down = Linear(params[self.names["down"]], self.ctx.products)
+        if self.has_bias:       # 32-bit, in the fused product's order of rows
+            bg, bu = params[self.names["gate_bias"]].float(), params[self.names["up_bias"]].float()
+            if self.interleave:
+                k = self.interleave
+                fused_b = torch.stack([bg.view(-1, k), bu.view(-1, k)], dim=1).reshape(-1)
+            else:
+                fused_b = torch.cat([bg, bu])
+            self.gate_up_bias = fused_b.contiguous()
+            self.down_bias = params[self.names["down_bias"]].float().contiguous()
 
     def kernel_modules(self):
         return ("elementwise",) + self.gate_up.kernel_modules() + self.down.kernel_modules()
@@ -142,6 +165,17 @@ class GatedMLP(FeedForward):
         return True
 
     def forward(self, x, step):
+        if self.has_bias:
+            sums = self.gate_up(x, out_dtype=torch.float32)
+            inner = ops.bias_gate_mul(sums, self.gate_up_bias, self.activation, self.ctx.dtype,
+                                      self.interleave)
+            d = self.down(inner, out_dtype=torch.float32, partial_ok=True)
+            # partial sums: the bias joins the first; else one 32-bit term for the norm to add
+            d = d if d.dim() == 3 else d.unsqueeze(0)
+            ops.add_bias_(d[0], self.down_bias)
+            return d
+        if self.activation == "relu":
+            return self.down(ops.relu_mul(self.gate_up(x), self.interleave), partial_ok=True)
         return self.down(self.gate_up.silu_mul(x, self.interleave, self.activation), partial_ok=True)
 
 
@@ -150,26 +184,35 @@ class RoutedExperts(FeedForward):
     """``n_experts`` small gated feed-forwards of which every token uses ``top``.
 
         z = Wr x (32-bit), s = softmax(z) over all n_experts + n_identity outputs
-        c = s + correction;  the outputs form ``n_groups`` equal groups of neighbours,
+        (``score_fn`` "sigmoid": s = sigmoid(z), every output by itself)
+        c = s + correction (``correction`` False: there is none, c = s);  the outputs form ``n_groups`` equal groups of neighbours,
         a group's score is its largest c, only outputs of the ``keep_groups`` best
         groups can be chosen; the ``top`` largest c are chosen and weigh in with s
         expert:  g = min(Wg x, limit), u = clamp(Wu x, -limit, limit),
                  y = Wd (g sigmoid(gate_slope g) (u + 1))
         the last ``n_identity`` outputs stand for experts that return x itself
         out = sum of s * y over the chosen; the weights are not renormalised
+        ``limit`` None clamps nothing; ``up_offset`` is the 1 of (u + 1);
+        ``weigh_input``: the weight multiplies the expert's input instead of its
+        result, out = sum of expert(s x)
 
     Tensors: ``router`` [n_experts + n_identity, hidden], ``correction``, and per
     expert j ``e<j>.gate`` / ``e<j>.up`` [intermediate, hidden], ``e<j>.down``.  The
     result leaves as ``top`` weighted 32-bit partial sums, which the next norm adds."""
 
     def __init__(self, ctx: BuildContext, hidden: int, intermediate: int, n_experts: int, top: int,
-                 limit: float, gate_slope: float, n_identity: int = 0, n_groups: int = 1,
-                 keep_groups: int = 1):
+                 limit: Optional[float], gate_slope: float, n_identity: int = 0, n_groups: int = 1,
+                 keep_groups: int = 1, score_fn: str = "softmax", correction: bool = True,
+                 weigh_input: bool = False, up_offset: float = 1.0):
         super().__init__(ctx)
         self.hidden, self.intermediate = int(hidden), int(intermediate)
         self.E, self.n_identity, self.top = int(n_experts), int(n_identity), int(top)
         self.n_groups, self.keep_groups = int(n_groups), int(keep_groups)
-        self.limit, self.gate_slope = float(limit), float(gate_slope)
+        self.limit = math.inf if limit is None else float(limit)
+        self.gate_slope, self.up_offset = float(gate_slope), float(up_offset)
+        if score_fn not in ("softmax", "sigmoid"):
+            raise ValueError(f"score function '{score_fn}': softmax or sigmoid")
+        self.score_fn, self.has_correction, self.weigh_input = score_fn, bool(correction), bool(weigh_input)
         n_all = self.E + self.n_identity
         if n_all % self.n_groups or not 1 <= self.keep_groups <= self.n_groups:
             raise ValueError(f"{n_all} router outputs do not form {self.n_groups} equal groups "
@@ -180,8 +223,9 @@ class RoutedExperts(FeedForward):
 
     def param_specs(self):
         n_all = self.E + self.n_identity
-        specs = {"router": ParamSpec((n_all, self.hidden)),
-                 "correction": ParamSpec((n_all,), "offset")}
+        specs = {"router": ParamSpec((n_all, self.hidden))}
+        if self.has_correction:
+            specs["correction"] = ParamSpec((n_all,), "offset")
         for j in range(self.E):
             specs[f"e{j}.gate"] = ParamSpec((self.intermediate, self.hidden))
             specs[f"e{j}.up"] = ParamSpec((self.intermediate, self.hidden))
@@ -191,7 +235,7 @@ class RoutedExperts(FeedForward):
     def load(self, params):
         # the router is 32-bit whatever the checkpoint stores
         self.router_w = params["router"].float().contiguous()
-        self.correction = params["correction"].float().contiguous()
+        self.correction = params["correction"].float().contiguous() if self.has_correction else None
         stack = lambda what: torch.stack([params[f"e{j}.{what}"] for j in range(self.E)]).to(
             self.ctx.dtype).contiguous()
         self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
@@ -206,4 +250,5 @@ class RoutedExperts(FeedForward):
         return ops.moe_forward(x, self.router_w, self.correction, self.w_gate, self.w_up,
                                self.w_down, top=self.top, n_identity=self.n_identity,
                                n_groups=self.n_groups, keep_groups=self.keep_groups,
-                               limit=self.limit, slope=self.gate_slope)
+                               limit=self.limit, slope=self.gate_slope, score_fn=self.score_fn,
+                               weigh_input=self.weigh_input, up_offset=self.up_offset)

@@ -22,11 +22,16 @@ class Embedding(Part):
 
 @register_part("embedding", "token")
 class TokenEmbedding(Embedding):
-    """x[t] = E[ids[t]], no scaling (src/training.rs:278-282)."""
+    """x[t] = E[ids[t]], no scaling (src/training.rs:278-282).  With ``scale`` the row
+    is multiplied by that constant in 32-bit, and the result is the 32-bit residual
+    stream itself (``starts_stream``) instead of a first contribution to it."""
 
-    def __init__(self, ctx: BuildContext, vocab: int, hidden: int, name: str = "weight"):
+    def __init__(self, ctx: BuildContext, vocab: int, hidden: int, name: str = "weight",
+                 scale: Optional[float] = None):
         super().__init__(ctx)
         self.vocab, self.hidden, self.name = int(vocab), int(hidden), name
+        self.scale = None if scale is None else float(scale)
+        self.starts_stream = self.scale is not None
         self.weight = None
 
     def param_specs(self):
@@ -42,6 +47,8 @@ class TokenEmbedding(Embedding):
         return True
 
     def forward(self, tokens, step):
+        if self.scale is not None:
+            return ops.embed_scaled(self.weight, tokens, self.scale)
         x = ops.embed(self.weight, tokens)
         return ops.cast(x, self.ctx.dtype) if x.dtype != self.ctx.dtype else x
 

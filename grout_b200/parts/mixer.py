@@ -218,3 +218,105 @@ class GQAAttention(Mixer):
                              page=cache.page, scale=self.scale, window=self.window,
                              softcap=self.softcap, sinks=self.sink)
         return self.o(attn.view(T, self.nq * self.Ds), partial_ok=True)
+
+
+@register_part("mixer", "latent_attention")
+class LatentAttention(Mixer):
+    """Attention whose keys and values are expanded from one latent vector per token.
+
+        q = Wq h                      per head ``head_dim`` plain and ``rot_dim`` rotated elements
+        d = Wdkv h                    ``kv_rank`` + ``rot_dim`` numbers
+        c = rmsnorm(d[:kv_rank]) * w  the latent (``norm_eps`` under the root)
+        k_rot = rot(d[kv_rank:])      one rotated key part shared by all heads
+        head i:  k = [Wuk_i c | k_rot],  v = Wuv_i c  (``v_head_dim``)
+        score = (q_plain . Wuk_i c + rot(q_rot) . k_rot) * scale;  softmax over the keys the
+        query sees (its own position and the ``window`` - 1 before it, or all before it)
+        y = Wo [ heads * sigmoid(Wg h) ]           (the gate only with ``gated``)
+
+    The cache keeps [c | k_rot] per token, once for all heads; Wuk is folded into
+    the query ((Wuk_i^T q_plain) . c) and Wuv applied to the attention's output over
+    the latents, so the attention kernels see query heads that all read one kv head of
+    kv_rank + rot_dim elements whose values are its keys.  ``position`` rotates the
+    rot_dim part (neighbouring pairs).  Norm, rotation and gate are 32-bit on the
+    projection's 32-bit sums.  ``names`` replaces local tensor names (keys q, dkv,
+    dkv_norm, uk, uv, g, o)."""
+
+    NAMES = {"q": "q", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv", "g": "g", "o": "o"}
+
+    def __init__(self, ctx: BuildContext, hidden: int, n_heads: int, head_dim: int, rot_dim: int,
+                 v_head_dim: int, kv_rank: int, position: PartSpec, scale: float, norm_eps: float,
+                 window: Optional[int] = None, gated: bool = True, names: Optional[dict] = None):
+        super().__init__(ctx)
+        self.hidden, self.H, self.dn, self.dr = int(hidden), int(n_heads), int(head_dim), int(rot_dim)
+        self.dv, self.R = int(v_head_dim), int(kv_rank)
+        self.scale, self.norm_eps = float(scale), float(norm_eps)
+        self.window = int(window) if window else None
+        self.gated = bool(gated)
+        self.names = dict(self.NAMES, **(names or {}))
+        self.position = build_part("position", position, ctx)
+        rot = self.position.rotary()
+        if self.dr and (rot is None or not rot.interleaved or rot.rot_dim != self.dr):
+            raise ValueError("latent attention rotates the whole rotated part in neighbouring pairs")
+        # the width of a cached row, of a query and of the attention's output
+        self.Ds = self.R + self.dr
+        if ctx.dtype == torch.bfloat16:           # the tensor-core kernels take multiples of 16
+            self.Ds = (self.Ds + 15) // 16 * 16
+        self.proj = self.o = self.uk_t = self.uv = self.norm_w = None
+
+    def children(self):
+        return (self.position,)
+
+    def param_specs(self):
+        W, H, nm = self.hidden, self.H, self.names
+        specs = {nm["q"]: ParamSpec((H * (self.dn + self.dr), W)),
+                 nm["dkv"]: ParamSpec((self.R + self.dr, W)),
+                 nm["dkv_norm"]: ParamSpec((self.R,), "vector"),
+                 nm["uk"]: ParamSpec((H * self.dn, self.R)), nm["uv"]: ParamSpec((H * self.dv, self.R)),
+                 nm["o"]: ParamSpec((W, H * self.dv))}
+        if self.gated:
+            specs[nm["g"]] = ParamSpec((H * self.dv, W))
+        return specs
+
+    def load(self, params):
+        nm = self.names
+        ws = [params[nm["q"]], params[nm["dkv"]]] + ([params[nm["g"]]] if self.gated else [])
+        if len({w.dtype for w in ws}) != 1:
+            raise ValueError("the projections of one mixer must be stored in one dtype to be fused")
+        self.proj = Linear(torch.cat(ws, dim=0), self.ctx.products)
+        self.o = Linear(params[nm["o"]], self.ctx.products)
+        dt = self.ctx.dtype
+        # [H dn, R] -> per head [R, dn]: the product that folds Wuk into the query
+        self.uk_t = params[nm["uk"]].view(self.H, self.dn, self.R).transpose(1, 2).to(dt).contiguous()
+        self.uv = params[nm["uv"]].view(self.H, self.dv, self.R).to(dt).contiguous()
+        self.norm_w = params[nm["dkv_norm"]].float().contiguous()
+
+    def kernel_modules(self):
+        mods = ("latent", "attn_generic") + self.proj.kernel_modules() + self.o.kernel_modules()
+        if self.ctx.dtype == torch.bfloat16:
+            mods += ops.fast_attention_modules(self.Ds, self.H, 1)
+        return mods
+
+    def cache_spec(self):
+        return KVSpec(1, self.Ds, self.window, values_in_keys=True)
+
+    def captures_prompts(self):
+        return True
+
+    def forward(self, x, step, cache):
+        if cache is None or cache.spec != self.cache_spec():
+            raise ValueError(f"latent attention with rows of {self.Ds} was given the cache "
+                             f"{None if cache is None else cache.spec}")
+        T, H = x.shape[0], self.H
+        rot = self.position.rotary()
+        proj = self.proj(x, out_dtype=torch.float32)
+        q_plain, q = ops.latent_prepare(
+            proj, self.norm_w, rot.inv_freq if rot else None, H=H, dn=self.dn, dr=self.dr, R=self.R,
+            dv=self.dv if self.gated else 0, eps=self.norm_eps, token_seq=step.token_seq,
+            token_pos=step.token_pos, slots=step.slots, block_table=cache.block_table,
+            pages=cache.k_pages, page=cache.page, dtype=self.ctx.dtype)
+        ops.heads_mm(q_plain, self.uk_t, q)
+        attn = ops.attention(q, cache.k_pages, cache.v_pages, cache.block_table, step=step,
+                             page=cache.page, scale=self.scale, window=self.window)
+        y = ops.heads_mm(attn, self.uv, gate=proj if self.gated else None,
+                         gate_col=H * (self.dn + self.dr) + self.R + self.dr)
+        return self.o(y.view(T, H * self.dv), partial_ok=True)

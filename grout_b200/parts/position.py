@@ -27,6 +27,7 @@ from .base import BuildContext, Part, register_part
 class RotaryTable:
     inv_freq: torch.Tensor   # float32 [rot_dim / 2] on the device
     rot_dim: int
+    interleaved: bool = False   # element 2j goes with 2j + 1 instead of j with j + rot_dim / 2
 
 
 class PositionEncoding(Part):
@@ -100,3 +101,17 @@ class RotaryHalfSplit(PositionEncoding):
 
     def captures_prompts(self):
         return True
+
+
+@register_part("position", "rotary_interleaved")
+class RotaryInterleaved(RotaryHalfSplit):
+    """The same rotation with neighbours as pairs: element 2j goes with element
+    2j + 1, j < rot_dim / 2, and the pair turns by pos * inv_freq[j].  The kernels of
+    ``gqa_attention`` rotate half-split pairs only; the mixers that take this
+    encoding (``latent_attention``) rotate in a kernel of their own."""
+
+    def __init__(self, ctx: BuildContext, head_dim: int, theta: float,
+                 rot_dim: Optional[int] = None, scaling: Optional[dict] = None,
+                 exact_table: bool = False):
+        super().__init__(ctx, head_dim, theta, rot_dim, scaling, exact_table)
+        self._table.interleaved = True

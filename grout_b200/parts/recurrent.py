@@ -10,9 +10,10 @@ import torch
 
 from ..cache.spec import StateSpec
 from ..kernels import ops
-from .base import BuildContext, ParamSpec, register_part
+from .base import BuildContext, ParamSpec, PartSpec, build_part, register_part
 from .linear import Linear
 from .mixer import Mixer
+from .position import PositionEncoding
 
 
 @register_part("mixer", "gated_delta")
@@ -99,4 +100,162 @@ class GatedDelta(Mixer):
                               taps=self.taps, unit_eps=self.unit_eps, norm_eps=self.norm_eps,
                               token_seq=step.token_seq, cu_q=step.cu_q, slots=step.slots,
                               dtype=self.ctx.dtype, max_rows=step.max_q_len)
+        return self.o(y, partial_ok=True)
+
+
+@register_part("mixer", "retention")
+class Retention(Mixer):
+    """Linear attention with a fixed decay per head and neither softmax nor
+    denominator.  With h the mixer's input,
+
+        q = Wq h, k = Wk h  (n_heads x key_dim),  v = Wv h  (n_heads x value_dim)
+        q, k rotated by ``position`` (a rotation of half-split pairs), k then times ``k_scale``
+        S <- decay_i S + k v^T;  o = S^T q                                    per head i
+        y = Wo [ o / sqrt(mean(o^2) + norm_eps) * silu(Wg h) ]                (no norm weight)
+
+    ``decay`` holds one constant per head.  S [key_dim, value_dim] starts at zero and
+    is kept per sequence in 32-bit.  The four projections are one product, which leaves
+    32-bit sums; all that follows up to y is 32-bit whatever the activation type.
+    ``names`` replaces local tensor names (keys q, k, v, g, o)."""
+
+    NAMES = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o"}
+
+    def __init__(self, ctx: BuildContext, hidden: int, n_heads: int, key_dim: int, value_dim: int,
+                 decay, position: PartSpec, norm_eps: float, k_scale: float = None, names=None):
+        super().__init__(ctx)
+        self.hidden, self.H, self.dk, self.dv = int(hidden), int(n_heads), int(key_dim), int(value_dim)
+        self.decay_values = tuple(float(d) for d in decay)
+        if len(self.decay_values) != self.H:
+            raise ValueError(f"{len(self.decay_values)} decays for {self.H} heads")
+        self.norm_eps = float(norm_eps)
+        self.k_scale = float(k_scale) if k_scale is not None else self.dk ** -0.5
+        self.names = dict(self.NAMES, **(names or {}))
+        self.position = build_part("position", position, ctx)
+        rot = self.position.rotary()
+        if rot is None and type(self.position).apply_qk is not PositionEncoding.apply_qk:
+            raise ValueError("retention takes a rotation (or no position encoding)")
+        if rot is not None and (rot.interleaved or rot.rot_dim > self.dk):
+            raise ValueError("retention rotates half-split pairs within a head's keys")
+        self.proj = self.o = self.decay = None
+
+    def children(self):
+        return (self.position,)
+
+    def param_specs(self):
+        W, H, dk, dv, nm = self.hidden, self.H, self.dk, self.dv, self.names
+        return {nm["q"]: ParamSpec((H * dk, W)), nm["k"]: ParamSpec((H * dk, W)),
+                nm["v"]: ParamSpec((H * dv, W)), nm["g"]: ParamSpec((H * dv, W)),
+                nm["o"]: ParamSpec((W, H * dv))}
+
+    def load(self, params):
+        nm = self.names
+        ws = [params[nm[k]] for k in ("q", "k", "v", "g")]
+        if len({w.dtype for w in ws}) != 1:
+            raise ValueError("the projections of one mixer must be stored in one dtype to be fused")
+        self.proj = Linear(torch.cat(ws, dim=0), self.ctx.products)
+        self.o = Linear(params[nm["o"]], self.ctx.products)
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float32, device=ws[0].device)
+
+    def kernel_modules(self):
+        return ("retention",) + self.proj.kernel_modules() + self.o.kernel_modules()
+
+    def cache_spec(self):
+        return StateSpec((self.H * self.dk * self.dv,), torch.float32)
+
+    def captures_prompts(self):
+        return True
+
+    def forward(self, x, step, cache):
+        if cache is None or tuple(cache.spec.shape) != tuple(self.cache_spec().shape):
+            raise ValueError(f"retention was given the cache {None if cache is None else cache.spec}")
+        rot = self.position.rotary()
+        proj = self.proj(x, out_dtype=torch.float32)
+        y = ops.retention_forward(proj, cache.state, self.decay, rot.inv_freq if rot else None,
+                                  H=self.H, dk=self.dk, dv=self.dv, rot_dim=rot.rot_dim if rot else 0,
+                                  k_scale=self.k_scale, norm_eps=self.norm_eps,
+                                  token_pos=step.token_pos, cu_q=step.cu_q, slots=step.slots,
+                                  dtype=self.ctx.dtype)
+        return self.o(y, partial_ok=True)
+
+
+@register_part("mixer", "gated_linear_recurrence")
+class GatedLinearRecurrence(Mixer):
+    """The recurrent block of Griffin: two branches of ``width`` channels,
+
+        y = gelu_tanh(Wy h + by);   u = conv(Wx h + bx)
+        (a causal convolution per channel of ``conv_taps`` taps with a bias, zeros
+        before the sequence's start, the last tap the current token's, no activation)
+        r = sigmoid(Wa_b u_b + ba),  i = sigmoid(Wi_b u_b + bi)
+        (the channels form ``blocks`` equal parts, part b with square matrices of its own)
+        a = exp(-log_decay_factor r softplus(lam));   S <- a S + sqrt(1 - a^2) i u
+        out = Wo (S * y)
+
+    S starts at zero (the first token is no special case) and is kept per sequence in
+    32-bit together with the convolution's last ``conv_taps - 1`` inputs.  The two
+    branches are one product that leaves 32-bit sums; all that follows up to S * y is
+    32-bit.  ``names`` replaces local tensor names (keys y, y_bias, x, x_bias, conv,
+    conv_bias, a, a_bias, i, i_bias, lam, o)."""
+
+    NAMES = {"y": "y", "y_bias": "y.b", "x": "x", "x_bias": "x.b", "conv": "conv",
+             "conv_bias": "conv.b", "a": "ra", "a_bias": "ra.b", "i": "ri", "i_bias": "ri.b",
+             "lam": "lam", "o": "o"}
+
+    def __init__(self, ctx: BuildContext, hidden: int, width: int, blocks: int, conv_taps: int,
+                 log_decay_factor: float = 8.0, names=None):
+        super().__init__(ctx)
+        self.hidden, self.C, self.blocks, self.taps = int(hidden), int(width), int(blocks), int(conv_taps)
+        if self.blocks < 1 or self.C % self.blocks:
+            raise ValueError(f"{self.C} channels do not form {self.blocks} equal parts")
+        if self.taps < 1:
+            raise ValueError("a convolution has at least one tap")
+        self.factor = float(log_decay_factor)
+        self.names = dict(self.NAMES, **(names or {}))
+        self.proj = self.o = None
+        self.bias = self.conv_w = self.conv_b = self.wa_t = self.wi_t = self.ba = self.bi = self.lam = None
+
+    def param_specs(self):
+        W, C, nb, nm = self.hidden, self.C, self.blocks, self.names
+        bw = C // nb
+        return {nm["y"]: ParamSpec((C, W)), nm["y_bias"]: ParamSpec((C,), "offset"),
+                nm["x"]: ParamSpec((C, W)), nm["x_bias"]: ParamSpec((C,), "offset"),
+                nm["conv"]: ParamSpec((C, self.taps), "vector"), nm["conv_bias"]: ParamSpec((C,), "offset"),
+                nm["a"]: ParamSpec((nb, bw, bw)), nm["a_bias"]: ParamSpec((nb, bw), "offset"),
+                nm["i"]: ParamSpec((nb, bw, bw)), nm["i_bias"]: ParamSpec((nb, bw), "offset"),
+                nm["lam"]: ParamSpec((C,), "offset"), nm["o"]: ParamSpec((W, C))}
+
+    def load(self, params):
+        nm = self.names
+        wy, wx = params[nm["y"]], params[nm["x"]]
+        if wy.dtype != wx.dtype:
+            raise ValueError("the two branches must be stored in one dtype to be fused")
+        self.proj = Linear(torch.cat([wy, wx], dim=0), self.ctx.products)
+        self.o = Linear(params[nm["o"]], self.ctx.products)
+        # what enters the recurrence is 32-bit whatever the checkpoint stores
+        f32 = lambda t: t.float().contiguous()
+        self.bias = f32(torch.cat([params[nm["y_bias"]].float(), params[nm["x_bias"]].float()]))
+        self.conv_w, self.conv_b = f32(params[nm["conv"]]), f32(params[nm["conv_bias"]])
+        # [part, out, in] -> [part, in, out]: a warp's threads read neighbouring outputs
+        self.wa_t = f32(params[nm["a"]].float().transpose(1, 2))
+        self.wi_t = f32(params[nm["i"]].float().transpose(1, 2))
+        self.ba, self.bi = f32(params[nm["a_bias"]].reshape(-1)), f32(params[nm["i_bias"]].reshape(-1))
+        self.lam = f32(params[nm["lam"]])
+
+    def kernel_modules(self):
+        return ("rglru",) + self.proj.kernel_modules() + self.o.kernel_modules()
+
+    def cache_spec(self):
+        return StateSpec((self.taps * self.C,), torch.float32)
+
+    def captures_prompts(self):
+        return True
+
+    def forward(self, x, step, cache):
+        if cache is None or tuple(cache.spec.shape) != tuple(self.cache_spec().shape):
+            raise ValueError(f"the gated linear recurrence was given the cache "
+                             f"{None if cache is None else cache.spec}")
+        proj = self.proj(x, out_dtype=torch.float32)
+        y = ops.rglru_forward(proj, cache.state, self.bias, self.conv_w, self.conv_b, self.wa_t,
+                              self.ba, self.wi_t, self.bi, self.lam, blocks=self.blocks,
+                              taps=self.taps, factor=self.factor, token_seq=step.token_seq,
+                              cu_q=step.cu_q, slots=step.slots, dtype=self.ctx.dtype)
         return self.o(y, partial_ok=True)
