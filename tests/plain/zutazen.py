@@ -52,6 +52,8 @@ def rotate(x, positions, base, dims, interleaved):
     p * base^(-2i/dims).  Element i goes with element i + dims/2, or, when
     ``interleaved``, element 2i with element 2i + 1."""
     x = x.to(DT).clone()
+    if not dims:
+        return x
     half = dims // 2
     f = torch.tensor([float(base) ** (-2.0 * i / dims) for i in range(half)], dtype=DT)
     ang = torch.as_tensor(positions, dtype=DT)[:, None] * f[None, :]         # [T, half]
@@ -154,7 +156,8 @@ def latent_attention_mixer(h, W, prefix, m, eps, first_pos=0):
     g = lambda n: W[prefix + n].to(DT)
     T = h.shape[0]
     pos = torch.arange(first_pos, first_pos + T)
-    rot = m["rot"]
+    rot = m.get("rot") or {"base": 1.0, "dims": 0}
+    window = m["mask"]["size"] if m.get("mask") else T + 1
     q = (h @ g("q").T).view(T, H, dn + dr)
     q_plain, q_rot = q[..., :dn], rotate(q[..., dn:], pos, rot["base"], rot["dims"], True)
     down = h @ g("dkv").T
@@ -167,7 +170,7 @@ def latent_attention_mixer(h, W, prefix, m, eps, first_pos=0):
     for i in range(H):
         qi = torch.cat([q_plain[:, i], q_rot[:, i]], dim=-1)
         ki = torch.cat([k_plain[:, i], k_rot], dim=-1)
-        outs.append(windowed_softmax_attention(qi, ki, v[:, i], m["scale"], m["mask"]["size"]) * gate[:, i])
+        outs.append(windowed_softmax_attention(qi, ki, v[:, i], m["scale"], window) * gate[:, i])
     return torch.cat(outs, dim=-1) @ g("o").T
 
 
@@ -223,3 +226,20 @@ def forward(tokens, W, cfg, return_layers=False):
         after.append(x)
     logits = rms_norm(x, W["final.norm"], eps) @ W["head"].to(DT).T
     return (logits, torch.stack(after)) if return_layers else logits
+
+
+def logits(W, cfg, tokens, rows=None):
+    out = forward(list(tokens), W, cfg)
+    return out if rows is None else out[list(rows)]
+
+
+def greedy_generate(W, cfg, prompt, n_new, stop_ids=()):
+    """The plain loop: the whole sequence is recomputed for every new token."""
+    seq, made = list(prompt), []
+    for _ in range(n_new):
+        tok = int(torch.argmax(forward(seq, W, cfg)[-1]))
+        made.append(tok)
+        seq.append(tok)
+        if tok in stop_ids:
+            break
+    return made
