@@ -21,7 +21,7 @@ weights, far more than the 126 MB L2, so nothing is flushed between timed steps.
                                        decode steps (launched one by one, an event pair
                                        around each): calls, time, GB/s, TFLOP/s, fractions
     python bench.py --requests S       the reference's request grid
-    python bench.py --designs [--design suvazen|sonalorn] [--design-sizes 1b,4b,8b] [--batch B] [--design-ops]
+    python bench.py --designs [--design suvazen|sonalorn|zutazen] [--design-sizes 1b,4b,8b] [--batch B] [--design-ops]
                                        prefill and decode throughput of the Suvazen (or Sonalorn)
                                        design beside the Qwen3 decoder at equal layer sizes (random weights), and
                                        with --design-ops the per-kernel tables of both
@@ -203,6 +203,30 @@ def sonalorn_config(size: str) -> dict:
                 layers=layers)
 
 
+def zutazen_config(size: str) -> dict:
+    """The Zutazen model of a size: the width, heads, head size, layers and vocabulary of
+    the Qwen3 model; the layers mix in turn by retention (as many heads as the attention
+    has, keys and values of the head size, decays from 1 - 2^-5 to 1 - 2^-10), by the
+    gated linear recurrence (as many channels as the stream, parts of a head's size, four
+    taps) and by latent attention (a latent of 96 and a rotated part of 32, which make a
+    cached row of the head size, a window of 1,024); every other layer has a dense
+    feed-forward of the same rows and the rest route two of eight experts of a quarter of
+    the rows each."""
+    W, nq, _nkv, D, I, L, V = DESIGN_SIZES[size]
+    ret = dict(heads=nq, dim=D, vdim=D, rot={"base": 1000000.0, "dims": D},
+               decay=[1.0 - 2.0 ** (-5.0 - 5.0 * h / max(nq - 1, 1)) for h in range(nq)])
+    rec = dict(width=W, blocks=W // D, conv=4)
+    lat = dict(heads=nq, dim=D, rot_dim=32, vdim=D, kv_rank=96, scale=(D + 32) ** -0.5,
+               rot={"base": 500000.0, "dims": 32}, mask={"size": 1024})
+    kinds = (("retention", ret), ("rglru", rec), ("latent_attention", lat))
+    dense = {"kind": "dense", "ff": I}
+    moe = {"kind": "moe", "expert": {"ff": I // 4 // 64 * 64}, "router": {"experts": 8, "top": 2}}
+    layers = [dict(type=kinds[i % 3][0], mixer=kinds[i % 3][1], mlp=dense if i % 2 == 0 else moe)
+              for i in range(L)]
+    return dict(architecture="Zutazen", vocab=V, width=W, norm={"eps": 1e-6}, embedding={"scale": W ** 0.5},
+                layers=layers)
+
+
 def design_configs(size: str, design: str = "suvazen"):
     W, nq, nkv, D, I, L, V = DESIGN_SIZES[size]
     qwen = dict(QWEN3_4B, hidden_size=W, num_attention_heads=nq, num_key_value_heads=nkv, head_dim=D,
@@ -216,6 +240,8 @@ def design_configs(size: str, design: str = "suvazen"):
                        for _ in range(L)])
     if design == "sonalorn":
         return {"qwen3": qwen, "sonalorn": sonalorn_config(size)}
+    if design == "zutazen":       # beside the attention model and beside the other design with state and experts
+        return {"qwen3": qwen, "sonalorn": sonalorn_config(size), "zutazen": zutazen_config(size)}
     return {"qwen3": qwen, "suvazen": suv}
 
 
@@ -501,7 +527,7 @@ def main() -> int:
     ap.add_argument("--designs", action="store_true",
                     help="instead of the default run: the Suvazen design beside the Qwen3 decoder at "
                          "equal layer sizes (--design-sizes), prefill and decode at --batch")
-    ap.add_argument("--design", default="suvazen", choices=["suvazen", "sonalorn"],
+    ap.add_argument("--design", default="suvazen", choices=["suvazen", "sonalorn", "zutazen"],
                     help="which design --designs sets beside Qwen3")
     ap.add_argument("--design-sizes", default="1b,4b,8b",
                     help=f"which of {sorted(DESIGN_SIZES)} --designs runs")

@@ -293,11 +293,24 @@ class LatentAttention(Mixer):
     def kernel_modules(self):
         mods = ("latent", "attn_generic") + self.proj.kernel_modules() + self.o.kernel_modules()
         if self.ctx.dtype == torch.bfloat16:
-            mods += ops.fast_attention_modules(self.Ds, self.H, 1)
+            mods += ops.fast_attention_modules(self.Ds, min(self.H, self.GROUP), 1)
         return mods
 
     def cache_spec(self):
         return KVSpec(1, self.Ds, self.window, values_in_keys=True)
+
+    GROUP = 16       # the most query heads that the tensor-core decode kernels let share a kv head
+
+    def _attend(self, q, step, cache):
+        """Attention of all heads over the one shared row per token.  More heads than the
+        tensor-core kernels let share a kv head go in groups, each a call of its own."""
+        kw = dict(step=step, page=cache.page, scale=self.scale, window=self.window)
+        if (self.H <= self.GROUP or q.dtype != torch.bfloat16
+                or not ops.fast_attention_takes(self.Ds, self.GROUP, 1, cache.page)):
+            return ops.attention(q, cache.k_pages, cache.v_pages, cache.block_table, **kw)
+        return torch.cat([ops.attention(q[:, a:a + self.GROUP].contiguous(), cache.k_pages, cache.v_pages,
+                                        cache.block_table, **kw)
+                          for a in range(0, self.H, self.GROUP)], dim=1)
 
     def captures_prompts(self):
         return True
@@ -315,8 +328,7 @@ class LatentAttention(Mixer):
             token_pos=step.token_pos, slots=step.slots, block_table=cache.block_table,
             pages=cache.k_pages, page=cache.page, dtype=self.ctx.dtype)
         ops.heads_mm(q_plain, self.uk_t, q)
-        attn = ops.attention(q, cache.k_pages, cache.v_pages, cache.block_table, step=step,
-                             page=cache.page, scale=self.scale, window=self.window)
+        attn = self._attend(q, step, cache)
         y = ops.heads_mm(attn, self.uv, gate=proj if self.gated else None,
                          gate_col=H * (self.dn + self.dr) + self.R + self.dr)
         return self.o(y.view(T, H * self.dv), partial_ok=True)

@@ -238,8 +238,8 @@ def greedy_generate(W, cfg, prompt, n_new, stop_ids=()):
     seq, made = list(prompt), []
     for _ in range(n_new):
         tok = int(torch.argmax(forward(seq, W, cfg)[-1]))
+        if tok in stop_ids:          # a stop token ends the request and is not part of its output
+            break
         made.append(tok)
         seq.append(tok)
-        if tok in stop_ids:
-            break
     return made
