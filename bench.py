@@ -452,7 +452,7 @@ def decode_timeline(eng, slots, V, g, pk, steps: int = 3) -> str:
                  and "memcpy" not in e.name.lower() and "memset" not in e.name.lower()),
                 key=lambda e: e.time_range.start)
     # a step begins with its embedding kernel, whichever the model has
-    starts = [i for i, e in enumerate(ev) if "embed_kernel" in e.name or "embed_pos_norm_kernel" in e.name]
+    starts = [i for i, e in enumerate(ev) if any(k in e.name for k in ("embed_kernel", "embed_pos_norm_kernel", "embed_scaled_kernel"))]
     rows, total = {}, 0.0
     for a, b in zip(starts, starts[1:] + [len(ev)]):
         frontier = ev[a].time_range.start
