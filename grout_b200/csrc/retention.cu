@@ -19,6 +19,11 @@
 // and written once per step, for sequences whose slot is not negative (padding
 // rows read zeros and store nothing).  `finish` normalises a head's read-out and
 // applies the gate.
+//
+// A step in which every sequence brings one row (decoding) is one kernel, `step`:
+// a block owns one (sequence, head), turns the row's q and k itself, streams the
+// head's whole state through once (a warp reads and writes whole rows of S), adds
+// up the warps' partial read-outs in shared memory and finishes the head.
 #include "common.cuh"
 
 struct RetentionArgs {
@@ -35,6 +40,7 @@ struct RetentionArgs {
   void* y;                // [T, H dv]
   int n_tokens, n_seqs, H, dk, dv, rot_dim;
   float k_scale, norm_eps;
+  int max_rows;           // the most rows a sequence brings (0: unknown)
 };
 
 #define RT_LANES 8      // lanes that share a column of the state
@@ -176,6 +182,112 @@ __global__ void __launch_bounds__(128) retention_finish_kernel(const RetentionAr
   }
 }
 
+#define RT_STEP_WARPS 8
+
+// One row per sequence.  DVJ: columns a lane holds (dv <= 32 DVJ).
+template <typename T, int DVJ>
+__global__ void __launch_bounds__(RT_STEP_WARPS * 32) retention_step_kernel(const RetentionArgs a) {
+  extern __shared__ float sm[];
+  __shared__ float scratch[32];
+  const int h = blockIdx.x, seq = blockIdx.y;
+  const int H = a.H, dk = a.dk, dv = a.dv, half = a.rot_dim / 2;
+  float* qs = sm;                      // [dk]
+  float* ks = qs + dk;                 // [dk]
+  float* vs = ks + dk;                 // [dv]
+  float* part = vs + dv;               // [RT_STEP_WARPS, dv]
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const float decay = a.decay[h];
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  const int t = a.cu_q[seq];
+  if (a.cu_q[seq + 1] - t <= 0) return;
+  const int C = 2 * H * dk + 2 * H * dv;
+  const float* row = a.proj + (size_t)t * C;
+  const float pos = (float)a.token_pos[t];
+  for (int e = tid; e < dk; e += blockDim.x) {
+    const float* q = row + h * dk;
+    const float* k = row + H * dk + h * dk;
+    if (e >= a.rot_dim) { qs[e] = q[e]; ks[e] = k[e] * a.k_scale; continue; }
+    if (e >= half) continue;
+    float sn, cs;
+    sincosf(pos * a.inv_freq[e], &sn, &cs);
+    qs[e] = q[e] * cs - q[e + half] * sn;
+    qs[e + half] = q[e + half] * cs + q[e] * sn;
+    ks[e] = (k[e] * cs - k[e + half] * sn) * a.k_scale;
+    ks[e + half] = (k[e + half] * cs + k[e] * sn) * a.k_scale;
+  }
+  for (int c = tid; c < dv; c += blockDim.x) vs[c] = row[2 * H * dk + h * dv + c];
+  __syncthreads();
+  const int slot = a.slots[seq];
+  float* sp = slot >= 0 ? a.state + (size_t)slot * a.state_stride + (size_t)h * dk * dv : nullptr;
+  float v[DVJ], acc[DVJ];
+#pragma unroll
+  for (int j = 0; j < DVJ; ++j) {
+    v[j] = lane + 32 * j < dv ? vs[lane + 32 * j] : 0.f;
+    acc[j] = 0.f;
+  }
+  // four rows of S a pass: all their loads are issued before the first is used
+  for (int i0 = w; i0 < dk; i0 += 4 * RT_STEP_WARPS) {
+    float S[4][DVJ];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int i = i0 + r * RT_STEP_WARPS;
+#pragma unroll
+      for (int j = 0; j < DVJ; ++j) {
+        const int c = lane + 32 * j;
+        S[r][j] = (sp && i < dk && c < dv) ? sp[(size_t)i * dv + c] : 0.f;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int i = i0 + r * RT_STEP_WARPS;
+      if (i >= dk) break;
+      const float ki = ks[i], qi = qs[i];
+#pragma unroll
+      for (int j = 0; j < DVJ; ++j) {
+        const int c = lane + 32 * j;
+        const float Sn = fmaf(decay, S[r][j], ki * v[j]);
+        if (sp && c < dv) sp[(size_t)i * dv + c] = Sn;
+        acc[j] = fmaf(Sn, qi, acc[j]);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < DVJ; ++j)
+    if (lane + 32 * j < dv) part[w * dv + lane + 32 * j] = acc[j];
+  __syncthreads();
+  pdl_launch_dependents_if_large();
+  // thread c finishes column c (and c + 256, ...): the warps' parts in a fixed order
+  float o[(DVJ * 32 + RT_STEP_WARPS * 32 - 1) / (RT_STEP_WARPS * 32)];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < (int)(sizeof(o) / sizeof(float)); ++j) {
+    const int c = tid + j * RT_STEP_WARPS * 32;
+    o[j] = 0.f;
+    if (c < dv) {
+      for (int ww = 0; ww < RT_STEP_WARPS; ++ww) o[j] += part[ww * dv + c];
+      ss = fmaf(o[j], o[j], ss);
+    }
+  }
+  const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)dv + a.norm_eps);
+  const float* g = row + 2 * H * dk + H * dv + h * dv;
+  T* y = (T*)a.y + ((size_t)t * H + h) * dv;
+#pragma unroll
+  for (int j = 0; j < (int)(sizeof(o) / sizeof(float)); ++j) {
+    const int c = tid + j * RT_STEP_WARPS * 32;
+    if (c < dv) {
+      const float gv = g[c];
+      y[c] = from_f32<T>(o[j] * inv * (gv / (1.0f + expf(-gv))));
+    }
+  }
+}
+
+template <typename T, int DVJ>
+static int retention_step_launch(const RetentionArgs& a, cudaStream_t s) {
+  const size_t smem = (size_t)(2 * a.dk + a.dv + RT_STEP_WARPS * a.dv) * sizeof(float);
+  return gb_launch(retention_step_kernel<T, DVJ>, dim3(a.H, a.n_seqs), dim3(RT_STEP_WARPS * 32), smem, s, a);
+}
+
 template <int KPL>
 static int retention_scan_launch(const RetentionArgs& a, cudaStream_t s) {
   return gb_launch(retention_scan_kernel<KPL>, dim3(a.H, a.n_seqs, (a.dv + RT_COLS - 1) / RT_COLS),
@@ -192,6 +304,12 @@ static int retention_forward(const RetentionArgs& a, cudaStream_t s) {
     return GB_ERR_BAD_ARG;
   if (a.dk > 256) return GB_ERR_UNSUPPORTED;
   if (a.n_tokens == 0 || a.n_seqs == 0) return 0;
+  if (a.max_rows == 1 && a.dv <= 256 && a.H <= 65535) {
+    if (a.dv <= 32) return retention_step_launch<T, 1>(a, s);
+    if (a.dv <= 64) return retention_step_launch<T, 2>(a, s);
+    if (a.dv <= 128) return retention_step_launch<T, 4>(a, s);
+    return retention_step_launch<T, 8>(a, s);
+  }
   int e = gb_launch(retention_rotate_kernel, dim3(a.n_tokens), dim3(256), 0, s, a);
   if (e) return e;
   const int kpl = (a.dk + RT_LANES - 1) / RT_LANES;

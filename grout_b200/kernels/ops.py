@@ -1486,7 +1486,7 @@ class _RetentionArgs(ctypes.Structure):
     _fields_ = [("proj", _P), ("decay", _P), ("inv_freq", _P), ("token_pos", _P), ("cu_q", _P),
                 ("slots", _P), ("state", _P), ("state_stride", _L), ("qk", _P), ("o", _P), ("y", _P),
                 ("n_tokens", _I), ("n_seqs", _I), ("H", _I), ("dk", _I), ("dv", _I), ("rot_dim", _I),
-                ("k_scale", _F), ("norm_eps", _F)]
+                ("k_scale", _F), ("norm_eps", _F), ("max_rows", _I)]
 
 
 def _cost_retention(out, proj, state, *a, H, dk, dv, **k):
@@ -1500,13 +1500,15 @@ def _cost_retention(out, proj, state, *a, H, dk, dv, **k):
 def retention_forward(proj: torch.Tensor, state: torch.Tensor, decay: torch.Tensor,
                       inv_freq: Optional[torch.Tensor], *, H: int, dk: int, dv: int, rot_dim: int,
                       k_scale: float, norm_eps: float, token_pos, cu_q, slots,
-                      dtype: torch.dtype) -> torch.Tensor:
+                      dtype: torch.dtype, max_rows: Optional[int] = None) -> torch.Tensor:
     """Retention on the rows of a step.  ``proj`` [T, 2 H dk + 2 H dv] 32-bit: the columns
     q | k | v | gate of the mixer's one projection; ``state`` [slots, H dk dv] 32-bit, updated
     in place for the sequences whose slot is not negative; ``decay`` [H] 32-bit; ``inv_freq``
     [rot_dim / 2] the rotation's frequencies (element i of a head goes with element
     i + rot_dim / 2).  Returns y [T, H dv] in ``dtype``: every head's read-out S^T q,
-    divided by its root mean square over dv (``norm_eps`` under the root), times silu(gate)."""
+    divided by its root mean square over dv (``norm_eps`` under the root), times silu(gate).
+    ``max_rows``: the most rows any sequence of the step brings, when the caller knows it (a
+    step of one row a sequence is one kernel)."""
     _need(proj, "projection", torch.float32, 2)
     _need(state, "state", torch.float32, 2)
     _need(decay, "decay", torch.float32, 1)
@@ -1536,6 +1538,7 @@ def retention_forward(proj: torch.Tensor, state: torch.Tensor, decay: torch.Tens
     a.qk, a.o, a.y = qk.data_ptr(), o.data_ptr(), y.data_ptr()
     a.n_tokens, a.n_seqs, a.H, a.dk, a.dv, a.rot_dim = T, n_seqs, H, dk, dv, int(rot_dim)
     a.k_scale, a.norm_eps = float(k_scale), float(norm_eps)
+    a.max_rows = int(max_rows) if max_rows else 0
     _check(_fn("retention", f"gb_retention_forward_{_suffix(dtype)}", "pp")(ctypes.addressof(a), _stream()),
            "retention_forward", 3)
     return y
@@ -1546,8 +1549,11 @@ class _RglruArgs(ctypes.Structure):
     _fields_ = [("proj", _P), ("bias", _P), ("conv_w", _P), ("conv_b", _P), ("wa_t", _P), ("ba", _P),
                 ("wi_t", _P), ("bi", _P), ("lam", _P), ("token_seq", _P), ("cu_q", _P), ("slots", _P),
                 ("state", _P), ("state_stride", _L), ("u", _P), ("ab", _P), ("out", _P),
+                ("chunks", _P), ("start", _P),
                 ("n_tokens", _I), ("n_seqs", _I), ("C", _I), ("blocks", _I), ("taps", _I),
-                ("factor", _F)]
+                ("factor", _F), ("max_rows", _I)]
+
+RGLRU_CHUNK = 64        # rows of a chunk of the recurrence's scan (RG_CHUNK of the kernel)
 
 
 def _cost_rglru(out, proj, state, *a, **k):
@@ -1561,14 +1567,16 @@ def _cost_rglru(out, proj, state, *a, **k):
 def rglru_forward(proj: torch.Tensor, state: torch.Tensor, bias: torch.Tensor, conv_w: torch.Tensor,
                   conv_b: torch.Tensor, wa_t: torch.Tensor, ba: torch.Tensor, wi_t: torch.Tensor,
                   bi: torch.Tensor, lam: torch.Tensor, *, blocks: int, taps: int, factor: float,
-                  token_seq, cu_q, slots, dtype: torch.dtype) -> torch.Tensor:
+                  token_seq, cu_q, slots, dtype: torch.dtype, max_rows: Optional[int] = None) -> torch.Tensor:
     """The gated linear recurrence on the rows of a step.  ``proj`` [T, 2 C] 32-bit: the
     columns y | x of the mixer's projection, ``bias`` [2 C] their biases; ``conv_w`` [C, taps]
     and ``conv_b`` [C] the convolution over x; ``wa_t``, ``wi_t`` [blocks, C / blocks, C / blocks]
     the gates' matrices per part of the channels, each stored [in, out], with biases ``ba``,
     ``bi`` [C]; ``lam`` [C]; the decay is exp(-factor * r * softplus(lam)).  ``state``
     [slots, taps * C] 32-bit: the last taps - 1 inputs of the convolution, then S; updated
-    in place for sequences whose slot is not negative.  Returns S * gelu_tanh(y) [T, C] in ``dtype``."""
+    in place for sequences whose slot is not negative.  ``max_rows``: the most rows any sequence
+    of the step brings, when the caller knows it (sequences of more than a chunk's rows are
+    scanned chunk by chunk).  Returns S * gelu_tanh(y) [T, C] in ``dtype``."""
     _need(proj, "projection", torch.float32, 2)
     _need(state, "state", torch.float32, 2)
     T, C2 = proj.shape
@@ -1594,13 +1602,17 @@ def rglru_forward(proj: torch.Tensor, state: torch.Tensor, bias: torch.Tensor, c
     u = torch.empty((T, C), dtype=torch.float32, device=dev)
     ab = torch.empty((T, 2, C), dtype=torch.float32, device=dev)
     out = torch.empty((T, C), dtype=dtype, device=dev)
+    chunks = torch.empty((T // RGLRU_CHUNK + n_seqs, 2, C), dtype=torch.float32, device=dev)
+    start = torch.empty((n_seqs, C), dtype=torch.float32, device=dev)
     a = _RglruArgs()
     a.proj, a.bias, a.conv_w, a.conv_b = proj.data_ptr(), bias.data_ptr(), conv_w.data_ptr(), conv_b.data_ptr()
     a.wa_t, a.ba, a.wi_t, a.bi, a.lam = wa_t.data_ptr(), ba.data_ptr(), wi_t.data_ptr(), bi.data_ptr(), lam.data_ptr()
     a.token_seq, a.cu_q, a.slots = token_seq.data_ptr(), cu_q.data_ptr(), slots.data_ptr()
     a.state, a.state_stride = state.data_ptr(), state.stride(0)
     a.u, a.ab, a.out = u.data_ptr(), ab.data_ptr(), out.data_ptr()
+    a.chunks, a.start = chunks.data_ptr(), start.data_ptr()
     a.n_tokens, a.n_seqs, a.C, a.blocks, a.taps, a.factor = T, n_seqs, C, int(blocks), int(taps), float(factor)
+    a.max_rows = int(max_rows) if max_rows else 0
     _check(_fn("rglru", f"gb_rglru_forward_{_suffix(dtype)}", "pp")(ctypes.addressof(a), _stream()),
            "rglru_forward", 3)
     return out

@@ -174,7 +174,7 @@ class Retention(Mixer):
                                   H=self.H, dk=self.dk, dv=self.dv, rot_dim=rot.rot_dim if rot else 0,
                                   k_scale=self.k_scale, norm_eps=self.norm_eps,
                                   token_pos=step.token_pos, cu_q=step.cu_q, slots=step.slots,
-                                  dtype=self.ctx.dtype)
+                                  dtype=self.ctx.dtype, max_rows=step.max_q_len)
         return self.o(y, partial_ok=True)
 
 
@@ -257,5 +257,6 @@ class GatedLinearRecurrence(Mixer):
         y = ops.rglru_forward(proj, cache.state, self.bias, self.conv_w, self.conv_b, self.wa_t,
                               self.ba, self.wi_t, self.bi, self.lam, blocks=self.blocks,
                               taps=self.taps, factor=self.factor, token_seq=step.token_seq,
-                              cu_q=step.cu_q, slots=step.slots, dtype=self.ctx.dtype)
+                              cu_q=step.cu_q, slots=step.slots, dtype=self.ctx.dtype,
+                              max_rows=step.max_q_len)
         return self.o(y, partial_ok=True)

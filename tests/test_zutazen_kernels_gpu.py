@@ -112,7 +112,7 @@ def _ret_run(w, m, xs, cuts, dtype, state=None, slot=0, n_slots=3, first_pos=0):
         proj = g32(xs[start - first_pos:start - first_pos + n].double() @ wp.T)
         y = ops.retention_forward(proj, state, decay, inv, H=H, dk=dk, dv=dv, rot_dim=rd, k_scale=dk ** -0.5,
                                   norm_eps=1e-5, token_pos=step.token_pos, cu_q=step.cu_q, slots=step.slots,
-                                  dtype=dtype)
+                                  dtype=dtype, max_rows=step.max_q_len)
         outs.append(y.float().cpu())
         start += n
     return torch.cat(outs), state
@@ -143,8 +143,8 @@ def test_retention_whole_in_portions_and_token_by_token(m):
     whole, _ = _ret_run(w, m, xs, [T], torch.float32)
     close(whole, want, torch.float32, "whole")
     for cuts in ([2] * 75, [1] * T, [1, 2, 3, 100, 44], [149, 1]):
-        got, _ = _ret_run(w, m, xs, cuts, torch.float32)
-        assert torch.equal(got, whole), cuts                  # the rows are walked one by one however they come
+        got, _ = _ret_run(w, m, xs, cuts, torch.float32)      # the same sums, in another order at most
+        close(got, whole, torch.float32, str(cuts))
     half, _ = _ret_run(w, m, xs, [T], torch.bfloat16)
     close(half, want, torch.bfloat16, "bfloat16 output")
 
@@ -173,16 +173,17 @@ def test_retention_batches_slots_used_again_and_padding():
     state = torch.zeros(4, H * dk * dv, device=DEV)
     run = lambda step, rows: ops.retention_forward(
         g32(rows.double() @ wp.T), state, decay, inv, H=H, dk=dk, dv=dv, rot_dim=16, k_scale=dk ** -0.5,
-        norm_eps=1e-5, token_pos=step.token_pos, cu_q=step.cu_q, slots=step.slots, dtype=torch.float32).cpu()
+        norm_eps=1e-5, token_pos=step.token_pos, cu_q=step.cu_q, slots=step.slots, dtype=torch.float32,
+        max_rows=step.max_q_len).cpu()
     # a in slot 2 and b in slot 1 start together with a padding sequence between them
     y = run(step_of([(2, 0, 30), (-1, 0, 3), (1, 0, 8)]), torch.cat([xa[:30], rnd(3, W, seed=8), xb[:8]]))
-    assert torch.equal(y[:30], alone_a[:30]) and torch.equal(y[33:], alone_b[:8])
+    close(y[:30], alone_a[:30], torch.float32); close(y[33:], alone_b[:8], torch.float32)
     assert float(state[3].abs().max()) == 0.0 and float(state[0].abs().max()) == 0.0   # padding rows store nothing
     y = run(step_of([(1, 8, 1), (2, 30, 1)]), torch.cat([xb[8:9], xa[30:31]]))         # decoded together, other order
-    assert torch.equal(y[0], alone_b[8]) and torch.equal(y[1], alone_a[30])
+    close(y[0], alone_b[8], torch.float32); close(y[1], alone_a[30], torch.float32)
     state[1].zero_()                                                  # b ends; its slot serves a new request
     y = run(step_of([(2, 31, 9), (1, 0, 9)]), torch.cat([xa[31:], xb]))
-    assert torch.equal(y[:9], alone_a[31:]) and torch.equal(y[9:], alone_b)
+    close(y[:9], alone_a[31:], torch.float32); close(y[9:], alone_b, torch.float32)
 
 
 def test_retention_reads_a_far_pair():
@@ -236,7 +237,7 @@ def _rec_run(w, m, xs, cuts, dtype, state=None, slot=0, n_slots=3):
                               g32(w["conv"]), g32(w["conv.b"]), g32(w["ra"].transpose(1, 2)), g32(w["ra.b"].reshape(-1)),
                               g32(w["ri"].transpose(1, 2)), g32(w["ri.b"].reshape(-1)), g32(w["lam"]), blocks=nb,
                               taps=taps, factor=8.0, token_seq=step.token_seq, cu_q=step.cu_q, slots=step.slots,
-                              dtype=dtype)
+                              dtype=dtype, max_rows=step.max_q_len)
         outs.append(y.float().cpu())
         start += n
     return torch.cat(outs), state
@@ -260,9 +261,9 @@ def test_recurrence_whole_in_portions_and_token_by_token(m):
     whole, _ = _rec_run(w, m, xs, [T], torch.float32)
     close(whole, want, torch.float32, "whole")
     # portions shorter than the convolution's tail, which then holds rows of several steps
-    for cuts in ([2] * 75, [1] * T, [1, 2, 3, 100, 44], [149, 1]):
+    for cuts in ([2] * 75, [1] * T, [1, 2, 3, 100, 44], [149, 1], [64, 65, 21], [33, 117]):
         got, _ = _rec_run(w, m, xs, cuts, torch.float32)
-        assert torch.equal(got, whole), cuts
+        close(got, whole, torch.float32, str(cuts))
     half, _ = _rec_run(w, m, xs, [T], torch.bfloat16)
     close(half, want, torch.bfloat16, "bfloat16 output")
 
@@ -302,15 +303,15 @@ def test_recurrence_batches_slots_used_again_and_padding():
         g32(rows.double() @ wp.T), state, g32(torch.cat([w["y.b"], w["x.b"]])), g32(w["conv"]), g32(w["conv.b"]),
         g32(w["ra"].transpose(1, 2)), g32(w["ra.b"].reshape(-1)), g32(w["ri"].transpose(1, 2)),
         g32(w["ri.b"].reshape(-1)), g32(w["lam"]), blocks=nb, taps=taps, factor=8.0, token_seq=step.token_seq,
-        cu_q=step.cu_q, slots=step.slots, dtype=torch.float32).cpu()
+        cu_q=step.cu_q, slots=step.slots, dtype=torch.float32, max_rows=step.max_q_len).cpu()
     y = run(step_of([(2, 0, 30), (-1, 0, 3), (1, 0, 8)]), torch.cat([xa[:30], rnd(3, W, seed=8), xb[:8]]))
-    assert torch.equal(y[:30], alone_a[:30]) and torch.equal(y[33:], alone_b[:8])
+    close(y[:30], alone_a[:30], torch.float32); close(y[33:], alone_b[:8], torch.float32)
     assert float(state[3].abs().max()) == 0.0                         # padding rows store nothing
     y = run(step_of([(1, 8, 1), (2, 30, 1)]), torch.cat([xb[8:9], xa[30:31]]))
-    assert torch.equal(y[0], alone_b[8]) and torch.equal(y[1], alone_a[30])
+    close(y[0], alone_b[8], torch.float32); close(y[1], alone_a[30], torch.float32)
     state[1].zero_()
     y = run(step_of([(2, 31, 9), (1, 0, 9)]), torch.cat([xa[31:], xb]))
-    assert torch.equal(y[:9], alone_a[31:]) and torch.equal(y[9:], alone_b)
+    close(y[:9], alone_a[31:], torch.float32); close(y[9:], alone_b, torch.float32)
 
 
 # ------------------------------------------------------------------ latent attention's pieces
@@ -383,3 +384,77 @@ def test_a_tokens_experts_do_not_depend_on_its_batch():
     for rows in ([0], [49, 3, 17], list(range(20, 37))):
         part, _, _ = _moe_run(w, E, top, x[rows], torch.float32)
         assert torch.equal(part.cpu(), whole[:, rows].cpu())
+
+
+# ------------------------------------------------------------------ steps of many rows, steps of one row
+def _rec_call(w, m, rows, step, state, dtype=torch.float32):
+    from grout_b200.kernels import ops
+    wp = torch.cat([w["y"], w["x"]], 0).double()
+    return ops.rglru_forward(
+        g32(rows.double() @ wp.T), state, g32(torch.cat([w["y.b"], w["x.b"]])), g32(w["conv"]), g32(w["conv.b"]),
+        g32(w["ra"].transpose(1, 2)), g32(w["ra.b"].reshape(-1)), g32(w["ri"].transpose(1, 2)),
+        g32(w["ri.b"].reshape(-1)), g32(w["lam"]), blocks=m["blocks"], taps=m["conv"], factor=8.0,
+        token_seq=step.token_seq, cu_q=step.cu_q, slots=step.slots, dtype=dtype, max_rows=step.max_q_len).float().cpu()
+
+
+@pytest.mark.parametrize("m", [dict(width=48, blocks=3, conv=4), dict(width=200, blocks=2, conv=2)])
+def test_recurrence_long_sequences_go_chunk_by_chunk(m):
+    """Sequences of more rows than a chunk of the scan, with lengths at a chunk's edge, in one
+    step beside short ones and a padding sequence: each as alone, the kept state as token by
+    token, and the next step goes on from it."""
+    W, C, taps = 24, m["width"], m["conv"]
+    w = _rec_weights(m, W, seed=11)
+    lens = [130, 1, 64, 65, 200, 63, 128]
+    xs = [rnd(n + 2, W, seed=20 + i) for i, n in enumerate(lens)]
+    want = [_rec_plain(w, m, x) for x in xs]
+    state = torch.zeros(len(lens) + 2, taps * C, device=DEV)
+    state[1:] = 7.0                                                # slots that held something else before
+    state[1:len(lens) + 1].zero_()
+    seqs = [(i + 1, 0, n) for i, n in enumerate(lens)]
+    seqs.insert(3, (-1, 0, 70))
+    rows = [x[:n] for x, n in zip(xs, lens)]
+    rows.insert(3, rnd(70, W, seed=40))
+    y = _rec_call(w, m, torch.cat(rows), step_of(seqs), state)
+    at = 0
+    for (slot, _, n) in seqs:
+        if slot > 0:
+            close(y[at:at + n], want[slot - 1][:n], torch.float32, f"length {n}")
+            _, by_one = _rec_run(w, m, xs[slot - 1][:n], [1] * n, torch.float32)
+            close(state[slot], by_one[0], torch.float32, f"state after {n}")
+        at += n
+    assert float((state[len(lens) + 1] - 7.0).abs().max()) == 0.0  # a padding sequence stores nothing
+    # two more rows each (a step of few rows) from the kept state
+    y = _rec_call(w, m, torch.cat([x[n:] for x, n in zip(xs, lens)]),
+                  step_of([(i + 1, n, 2) for i, n in enumerate(lens)]), state)
+    for i, n in enumerate(lens):
+        close(y[2 * i:2 * i + 2], want[i][n:], torch.float32, f"after {n}")
+
+
+@pytest.mark.parametrize("m", [_ret(3, 40, 20, 12), _ret(2, 64, 130, 64), _ret(1, 256, 256, 32), _ret(5, 8, 3, 2),
+                               _ret(2, 24, 300, 0)])
+def test_retention_step_of_one_row_a_sequence(m):
+    """A step in which every sequence brings one row against the same rows walked by the
+    kernels for steps of any shape: read-outs and states, a padding sequence among them."""
+    from grout_b200.kernels import ops
+    from grout_b200.parts.position import scaled_inverse_frequencies
+    H, dk, dv, W = m["heads"], m["dim"], m["vdim"], 24
+    rd = m["rot"]["dims"]
+    w = _ret_weights(m, W, seed=12)
+    wp = torch.cat([w[k] for k in ("q", "k", "v", "g")], 0).double()
+    inv = torch.from_numpy(scaled_inverse_frequencies(rd, m["rot"]["base"], None)).float().to(DEV) if rd else None
+    decay = torch.tensor(m["decay"], dtype=torch.float32, device=DEV)
+    starts = [5, 0, 700, 31]
+    step = step_of([(2, starts[0], 1), (-1, starts[1], 1), (0, starts[2], 1), (3, starts[3], 1)])
+    rows = rnd(4, W, seed=13)
+    before = rnd(5, H * dk * dv, seed=14).to(DEV)
+    outs = []
+    for max_rows in (None, 1):
+        state = before.clone()
+        y = ops.retention_forward(g32(rows.double() @ wp.T), state, decay, inv, H=H, dk=dk, dv=dv, rot_dim=rd,
+                                  k_scale=dk ** -0.5, norm_eps=1e-5, token_pos=step.token_pos, cu_q=step.cu_q,
+                                  slots=step.slots, dtype=torch.float32, max_rows=max_rows)
+        outs.append((y.cpu(), state.cpu()))
+    close(outs[1][0], outs[0][0], torch.float32, "read-outs")
+    close(outs[1][1], outs[0][1], torch.float32, "states")
+    assert torch.equal(outs[1][1][[1, 4]], before.cpu()[[1, 4]])      # slots of no sequence stay
+    assert not torch.equal(outs[1][1][0], before.cpu()[0])
