@@ -246,7 +246,7 @@ def design_configs(size: str, design: str = "suvazen"):
 
 
 def run_designs(sizes, batch: int, steps: int, warm: int, with_ops: bool, pk,
-                which: str = "suvazen") -> int:
+                which: str = "suvazen", only=None) -> int:
     """Prefill of one 2,048-token prompt and decode steps of ``batch`` sequences that hold such
     prompts, for both designs at each size: device times between CUDA events, the prompt step
     as the median of six after three, the decode steps as generation runs them (tokens chosen
@@ -258,6 +258,8 @@ def run_designs(sizes, batch: int, steps: int, warm: int, with_ops: bool, pk,
     for size in sizes:
         out[size] = {}
         for design, cfg in design_configs(size, which).items():
+            if only and design not in only:
+                continue
             V = cfg.get("vocab_size", cfg.get("vocab"))
             room = (PROMPT + warm + steps + 64 + 63) // 64 * 64
             eng = Engine.random(cfg, 0, dtype="bfloat16", max_tokens=batch * room, max_batch=batch,
@@ -531,6 +533,8 @@ def main() -> int:
                     help="which design --designs sets beside Qwen3")
     ap.add_argument("--design-sizes", default="1b,4b,8b",
                     help=f"which of {sorted(DESIGN_SIZES)} --designs runs")
+    ap.add_argument("--design-models", default=None,
+                    help="with --designs: run only these of the models it would run (comma-separated names)")
     ap.add_argument("--design-ops", action="store_true",
                     help="with --designs: also the per-kernel tables of a prompt step and a decode step")
     args = ap.parse_args()
@@ -550,8 +554,9 @@ def main() -> int:
         if any(x not in DESIGN_SIZES for x in sizes):
             print(f"bench.py: --design-sizes takes {sorted(DESIGN_SIZES)}", file=sys.stderr)
             return 2
+        only = [x for x in args.design_models.split(",") if x] if args.design_models else None
         return run_designs(sizes, args.batch, min(args.steps, 64), max(args.warmup, 3), args.design_ops,
-                           peaks(), args.design)
+                           peaks(), args.design, only)
     if args.prompt_len != PROMPT:
         if not 1 <= args.prompt_len <= 36864:
             print("bench.py: --prompt-len must be 1..36864", file=sys.stderr)

@@ -1540,7 +1540,7 @@ def retention_forward(proj: torch.Tensor, state: torch.Tensor, decay: torch.Tens
     a.k_scale, a.norm_eps = float(k_scale), float(norm_eps)
     a.max_rows = int(max_rows) if max_rows else 0
     _check(_fn("retention", f"gb_retention_forward_{_suffix(dtype)}", "pp")(ctypes.addressof(a), _stream()),
-           "retention_forward", 3)
+           "retention_forward", 1 if a.max_rows == 1 and dv <= 256 else 3)
     return y
 
 
@@ -1554,6 +1554,7 @@ class _RglruArgs(ctypes.Structure):
                 ("factor", _F), ("max_rows", _I)]
 
 RGLRU_CHUNK = 64        # rows of a chunk of the recurrence's scan (RG_CHUNK of the kernel)
+RGLRU_FEW_ROWS = 32     # up to this many rows the gates come from one kernel (RG_FEW of the kernel)
 
 
 def _cost_rglru(out, proj, state, *a, **k):
@@ -1613,8 +1614,10 @@ def rglru_forward(proj: torch.Tensor, state: torch.Tensor, bias: torch.Tensor, c
     a.chunks, a.start = chunks.data_ptr(), start.data_ptr()
     a.n_tokens, a.n_seqs, a.C, a.blocks, a.taps, a.factor = T, n_seqs, C, int(blocks), int(taps), float(factor)
     a.max_rows = int(max_rows) if max_rows else 0
+    most = min(a.max_rows, T) if a.max_rows else T
+    kernels = (1 if T <= RGLRU_FEW_ROWS else 2) + (1 if most <= RGLRU_CHUNK else 2)
     _check(_fn("rglru", f"gb_rglru_forward_{_suffix(dtype)}", "pp")(ctypes.addressof(a), _stream()),
-           "rglru_forward", 3)
+           "rglru_forward", kernels)
     return out
 
 
