@@ -20,6 +20,13 @@
 // rows read zeros and store nothing).  `finish` normalises a head's read-out and
 // applies the gate.
 //
+// A step in which a sequence brings RT_CHUNK_MIN rows or more goes chunk by chunk, five
+// kernels: `scan` walks every chunk of RT_CHUNK rows at the same time, each from zeros,
+// and leaves the chunk's read-outs within itself and what the chunk adds to the state;
+// `prefix` turns those into the states at the chunks' starts (S <- decay^rows S + added,
+// in the chunks' order) and stores the last; `cross` adds decay^(j+1) S_start^T q to row
+// j of every chunk, a tiled 32-bit product.
+//
 // A step in which every sequence brings one row (decoding) is one kernel, `step`:
 // a block owns one (sequence, head), turns the row's q and k itself, streams the
 // head's whole state through once (a warp reads and writes whole rows of S), adds
@@ -37,6 +44,7 @@ struct RetentionArgs {
   long long state_stride;
   float* qk;              // [T, 2, H, dk] scratch: turned q, turned and scaled k
   float* o;               // [T, H, dv] scratch: the read-outs
+  float* chunk_state;     // [T / RT_CHUNK + n_seqs, H, dk, dv] scratch of the chunked scan
   void* y;                // [T, H dv]
   int n_tokens, n_seqs, H, dk, dv, rot_dim;
   float k_scale, norm_eps;
@@ -46,6 +54,11 @@ struct RetentionArgs {
 #define RT_LANES 8      // lanes that share a column of the state
 #define RT_COLS 16      // columns a block owns
 #define RT_STAGE 16     // rows staged at a time
+#define RT_CHUNK 128    // rows of a chunk where a sequence brings more than that
+#define RT_TM 64        // rows of a block of the chunks' second pass
+#define RT_TN 128       // columns of its tile
+#define RT_TK 16        // elements of a head it stages at a time
+#define RT_CHUNK_MIN 256  // a step goes chunk by chunk when a sequence brings this many rows
 
 __global__ void __launch_bounds__(256) retention_rotate_kernel(const RetentionArgs a) {
   pdl_launch_dependents_if_small();
@@ -80,7 +93,15 @@ __device__ __forceinline__ int rt_row(int lane, int r) {
   return (KPL % 4 == 0) ? (r >> 2) * 32 + lane * 4 + (r & 3) : r * RT_LANES + lane;
 }
 
-template <int KPL>
+// Chunk z of a sequence is its rows z RT_CHUNK .. ; its matrices live at entry
+// (first row / RT_CHUNK + the sequence's number), which no other chunk has.
+__device__ __forceinline__ size_t rt_entry(int first, int z, int seq) {
+  return (size_t)((first + z * RT_CHUNK) / RT_CHUNK + seq);
+}
+
+// CHUNKED: blockIdx.z also counts the sequence's chunks; a block walks one chunk's rows
+// from a state of zeros and leaves what the chunk alone adds up to in the chunk's entry.
+template <int KPL, bool CHUNKED>
 __global__ void __launch_bounds__(RT_COLS* RT_LANES) retention_scan_kernel(const RetentionArgs a) {
   constexpr int DKP = KPL * RT_LANES;            // dk rounded up; the rest is zeros
   __shared__ __align__(16) float qs[RT_STAGE][DKP];
@@ -88,20 +109,33 @@ __global__ void __launch_bounds__(RT_COLS* RT_LANES) retention_scan_kernel(const
   __shared__ float vs[RT_STAGE][RT_COLS];
   pdl_launch_dependents_if_small();
   pdl_wait();
-  const int h = blockIdx.x, seq = blockIdx.y, c0 = blockIdx.z * RT_COLS;
   const int H = a.H, dk = a.dk, dv = a.dv;
-  const int first = a.cu_q[seq], n = a.cu_q[seq + 1] - first;
+  const int groups = (dv + RT_COLS - 1) / RT_COLS;
+  const int h = blockIdx.x, seq = blockIdx.y;
+  const int z = CHUNKED ? blockIdx.z / groups : 0;
+  const int c0 = (CHUNKED ? blockIdx.z % groups : blockIdx.z) * RT_COLS;
+  int first = a.cu_q[seq], n = a.cu_q[seq + 1] - first;
+  if (CHUNKED) {
+    if (z * RT_CHUNK >= n) return;
+    n = min(RT_CHUNK, n - z * RT_CHUNK);
+  }
   if (n <= 0) return;
   const int tid = threadIdx.x, lane = tid % RT_LANES, col = c0 + tid / RT_LANES;
   const bool live = col < dv;
-  const int slot = a.slots[seq];
-  float* sp = slot >= 0 ? a.state + (size_t)slot * a.state_stride + (size_t)h * dk * dv : nullptr;
+  float* sp;
+  if (CHUNKED) {
+    sp = a.chunk_state + (rt_entry(first, z, seq) * H + h) * dk * dv;
+    first += z * RT_CHUNK;
+  } else {
+    const int slot = a.slots[seq];
+    sp = slot >= 0 ? a.state + (size_t)slot * a.state_stride + (size_t)h * dk * dv : nullptr;
+  }
   const float decay = a.decay[h];
   float S[KPL];
 #pragma unroll
   for (int r = 0; r < KPL; ++r) {
     const int i = rt_row<KPL>(lane, r);
-    S[r] = (sp && live && i < dk) ? sp[(size_t)i * dv + col] : 0.f;
+    S[r] = (!CHUNKED && sp && live && i < dk) ? sp[(size_t)i * dv + col] : 0.f;
   }
   const int C = 2 * H * dk + 2 * H * dv;
   for (int t0 = 0; t0 < n; t0 += RT_STAGE) {
@@ -155,6 +189,102 @@ __global__ void __launch_bounds__(RT_COLS* RT_LANES) retention_scan_kernel(const
     for (int r = 0; r < KPL; ++r) {
       const int i = rt_row<KPL>(lane, r);
       if (i < dk) sp[(size_t)i * dv + col] = S[r];
+    }
+  }
+}
+
+// The states at the chunks' starts: a thread owns one element of a (sequence, head)'s
+// matrix, walks the chunks in order, leaves in every chunk's entry the state the chunk
+// starts from in place of what the chunk adds, and stores the state after the last.
+__global__ void __launch_bounds__(256) retention_prefix_kernel(const RetentionArgs a) {
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  const int h = blockIdx.y, seq = blockIdx.z, H = a.H;
+  const size_t per = (size_t)a.dk * a.dv;
+  const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int first = a.cu_q[seq], n = a.cu_q[seq + 1] - first;
+  if (e >= per || n <= 0) return;
+  const int slot = a.slots[seq];
+  float* sp = slot >= 0 ? a.state + (size_t)slot * a.state_stride + (size_t)h * per : nullptr;
+  const float decay = a.decay[h];
+  const float whole = powf(decay, (float)RT_CHUNK);
+  float S = sp ? sp[e] : 0.f;
+  const int nz = (n + RT_CHUNK - 1) / RT_CHUNK;
+  for (int z = 0; z < nz; ++z) {
+    float* p = a.chunk_state + (rt_entry(first, z, seq) * H + h) * per + e;
+    const float add = *p;
+    *p = S;
+    const int len = min(RT_CHUNK, n - z * RT_CHUNK);
+    S = fmaf(len == RT_CHUNK ? whole : powf(decay, (float)len), S, add);
+  }
+  pdl_launch_dependents_if_large();
+  if (sp) sp[e] = S;
+}
+
+// What the state at a chunk's start adds to the chunk's read-outs: row j of the chunk
+// gets decay^(j+1) S^T q.  A block owns RT_TM rows of one chunk and RT_TN columns of one
+// head; a thread owns 4 rows and 8 columns; the head's elements come RT_TK at a time.
+__global__ void __launch_bounds__(256) retention_cross_kernel(const RetentionArgs a) {
+  __shared__ __align__(16) float qs[RT_TK][RT_TM];
+  __shared__ __align__(16) float ss[RT_TK][RT_TN];
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  const int H = a.H, dk = a.dk, dv = a.dv;
+  const int col_tiles = (dv + RT_TN - 1) / RT_TN;
+  const int h = blockIdx.y, seq = blockIdx.z;
+  const int c0 = (blockIdx.x % col_tiles) * RT_TN;
+  const int tile = blockIdx.x / col_tiles;
+  const int z = tile / (RT_CHUNK / RT_TM), j0 = (tile % (RT_CHUNK / RT_TM)) * RT_TM;
+  const int first = a.cu_q[seq], n = a.cu_q[seq + 1] - first;
+  if (z * RT_CHUNK + j0 >= n) return;
+  const int rows = min(RT_TM, n - z * RT_CHUNK - j0);
+  const int r0 = first + z * RT_CHUNK + j0;
+  const float* S = a.chunk_state + (rt_entry(first, z, seq) * H + h) * (size_t)dk * dv;
+  const int tid = threadIdx.x, ty = tid / 16, tx = tid % 16;
+  float acc[4][8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < dk; k0 += RT_TK) {
+    __syncthreads();
+    {
+      const int m = tid / 4, kk = (tid % 4) * 4;
+      const float* src = a.qk + ((size_t)(r0 + m) * 2 * H + h) * dk + k0 + kk;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) qs[kk + i][m] = (m < rows && k0 + kk + i < dk) ? src[i] : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < RT_TK * RT_TN / 256; ++i) {
+      const int idx = tid + i * 256, kk = idx / RT_TN, c = idx % RT_TN;
+      ss[kk][c] = (k0 + kk < dk && c0 + c < dv) ? S[(size_t)(k0 + kk) * dv + c0 + c] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < RT_TK; ++kk) {
+      const float4 q4 = *reinterpret_cast<const float4*>(&qs[kk][ty * 4]);
+      const float4 s0 = *reinterpret_cast<const float4*>(&ss[kk][tx * 4]);
+      const float4 s1 = *reinterpret_cast<const float4*>(&ss[kk][64 + tx * 4]);
+      const float qv[4] = {q4.x, q4.y, q4.z, q4.w};
+      const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(qv[i], sv[j], acc[i][j]);
+    }
+  }
+  pdl_launch_dependents_if_large();
+  const float decay = a.decay[h];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = ty * 4 + i;
+    if (m >= rows) continue;
+    const float f = powf(decay, (float)(j0 + m + 1));
+    float* o = a.o + ((size_t)(r0 + m) * H + h) * dv;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int c = c0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + j - 4);
+      if (c < dv) o[c] = fmaf(f, acc[i][j], o[c]);
     }
   }
 }
@@ -289,9 +419,12 @@ static int retention_step_launch(const RetentionArgs& a, cudaStream_t s) {
 }
 
 template <int KPL>
-static int retention_scan_launch(const RetentionArgs& a, cudaStream_t s) {
-  return gb_launch(retention_scan_kernel<KPL>, dim3(a.H, a.n_seqs, (a.dv + RT_COLS - 1) / RT_COLS),
-                   dim3(RT_COLS * RT_LANES), 0, s, a);
+static int retention_scan_launch(const RetentionArgs& a, cudaStream_t s, int chunks) {
+  const int groups = (a.dv + RT_COLS - 1) / RT_COLS;
+  if (chunks)
+    return gb_launch(retention_scan_kernel<KPL, true>, dim3(a.H, a.n_seqs, chunks * groups),
+                     dim3(RT_COLS * RT_LANES), 0, s, a);
+  return gb_launch(retention_scan_kernel<KPL, false>, dim3(a.H, a.n_seqs, groups), dim3(RT_COLS * RT_LANES), 0, s, a);
 }
 
 template <typename T>
@@ -312,14 +445,27 @@ static int retention_forward(const RetentionArgs& a, cudaStream_t s) {
   }
   int e = gb_launch(retention_rotate_kernel, dim3(a.n_tokens), dim3(256), 0, s, a);
   if (e) return e;
+  // a sequence of many rows goes chunk by chunk: every chunk alone from zeros and all at
+  // once, then the states at the chunks' starts, then what those add to the read-outs
+  const int groups = (a.dv + RT_COLS - 1) / RT_COLS;
+  int chunks = a.max_rows >= RT_CHUNK_MIN && a.chunk_state ? (a.max_rows + RT_CHUNK - 1) / RT_CHUNK : 0;
+  if ((long long)chunks * groups > 65535 || (long long)chunks * (RT_CHUNK / RT_TM) * ((a.dv + RT_TN - 1) / RT_TN) > 0x7fffffffLL)
+    chunks = 0;
   const int kpl = (a.dk + RT_LANES - 1) / RT_LANES;
-  if (kpl <= 1) e = retention_scan_launch<1>(a, s);
-  else if (kpl <= 2) e = retention_scan_launch<2>(a, s);
-  else if (kpl <= 4) e = retention_scan_launch<4>(a, s);
-  else if (kpl <= 8) e = retention_scan_launch<8>(a, s);
-  else if (kpl <= 16) e = retention_scan_launch<16>(a, s);
-  else e = retention_scan_launch<32>(a, s);
+  if (kpl <= 1) e = retention_scan_launch<1>(a, s, chunks);
+  else if (kpl <= 2) e = retention_scan_launch<2>(a, s, chunks);
+  else if (kpl <= 4) e = retention_scan_launch<4>(a, s, chunks);
+  else if (kpl <= 8) e = retention_scan_launch<8>(a, s, chunks);
+  else if (kpl <= 16) e = retention_scan_launch<16>(a, s, chunks);
+  else e = retention_scan_launch<32>(a, s, chunks);
   if (e) return e;
+  if (chunks) {
+    e = gb_launch(retention_prefix_kernel, dim3((a.dk * a.dv + 255) / 256, a.H, a.n_seqs), dim3(256), 0, s, a);
+    if (e) return e;
+    e = gb_launch(retention_cross_kernel,
+                  dim3(chunks * (RT_CHUNK / RT_TM) * ((a.dv + RT_TN - 1) / RT_TN), a.H, a.n_seqs), dim3(256), 0, s, a);
+    if (e) return e;
+  }
   const long long warps = (long long)a.n_tokens * a.H;
   return gb_launch(retention_finish_kernel<T>, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, s, a);
 }

@@ -1484,9 +1484,14 @@ def delta_forward(proj: torch.Tensor, state: torch.Tensor, conv_w: torch.Tensor,
 # ---------------------------------------------------------------- retention
 class _RetentionArgs(ctypes.Structure):
     _fields_ = [("proj", _P), ("decay", _P), ("inv_freq", _P), ("token_pos", _P), ("cu_q", _P),
-                ("slots", _P), ("state", _P), ("state_stride", _L), ("qk", _P), ("o", _P), ("y", _P),
+                ("slots", _P), ("state", _P), ("state_stride", _L), ("qk", _P), ("o", _P), ("chunk_state", _P),
+                ("y", _P),
                 ("n_tokens", _I), ("n_seqs", _I), ("H", _I), ("dk", _I), ("dv", _I), ("rot_dim", _I),
                 ("k_scale", _F), ("norm_eps", _F), ("max_rows", _I)]
+
+
+RETENTION_CHUNK = 128        # rows of a chunk of the kernel's chunked scan
+RETENTION_CHUNK_MIN = 256    # a sequence of this many rows in a step: the step goes chunk by chunk
 
 
 def _cost_retention(out, proj, state, *a, H, dk, dv, **k):
@@ -1508,7 +1513,8 @@ def retention_forward(proj: torch.Tensor, state: torch.Tensor, decay: torch.Tens
     i + rot_dim / 2).  Returns y [T, H dv] in ``dtype``: every head's read-out S^T q,
     divided by its root mean square over dv (``norm_eps`` under the root), times silu(gate).
     ``max_rows``: the most rows any sequence of the step brings, when the caller knows it (a
-    step of one row a sequence is one kernel)."""
+    step of one row a sequence is one kernel; a step with a sequence of many rows runs all
+    chunks of 128 rows side by side and joins them through the states at their starts)."""
     _need(proj, "projection", torch.float32, 2)
     _need(state, "state", torch.float32, 2)
     _need(decay, "decay", torch.float32, 1)
@@ -1539,8 +1545,12 @@ def retention_forward(proj: torch.Tensor, state: torch.Tensor, decay: torch.Tens
     a.n_tokens, a.n_seqs, a.H, a.dk, a.dv, a.rot_dim = T, n_seqs, H, dk, dv, int(rot_dim)
     a.k_scale, a.norm_eps = float(k_scale), float(norm_eps)
     a.max_rows = int(max_rows) if max_rows else 0
+    chunked = a.max_rows >= RETENTION_CHUNK_MIN
+    if chunked:   # one matrix a head for every chunk of every sequence
+        chunk_state = torch.empty((T // RETENTION_CHUNK + n_seqs, H * dk * dv), dtype=torch.float32, device=dev)
+        a.chunk_state = chunk_state.data_ptr()
     _check(_fn("retention", f"gb_retention_forward_{_suffix(dtype)}", "pp")(ctypes.addressof(a), _stream()),
-           "retention_forward", 1 if a.max_rows == 1 and dv <= 256 else 3)
+           "retention_forward", 1 if a.max_rows == 1 and dv <= 256 else 5 if chunked else 3)
     return y
 
 

@@ -458,3 +458,55 @@ def test_retention_step_of_one_row_a_sequence(m):
     close(outs[1][1], outs[0][1], torch.float32, "states")
     assert torch.equal(outs[1][1][[1, 4]], before.cpu()[[1, 4]])      # slots of no sequence stay
     assert not torch.equal(outs[1][1][0], before.cpu()[0])
+
+
+@pytest.mark.parametrize("m", [_ret(3, 40, 20, 12), _ret(2, 64, 130, 64, lo=0.9), _ret(1, 128, 128, 128, lo=0.97),
+                               _ret(2, 20, 140, 0, lo=0.5, hi=0.9999)])
+def test_retention_long_sequences_go_chunk_by_chunk(m):
+    """Sequences of more rows than the chunks of the scan, with lengths at a chunk's edge, in
+    one step beside short ones and a padding sequence, from states that an earlier portion
+    left: each as alone in the plain implementation, the read-outs and the kept states as
+    the row-by-row kernels give them, and a step of few rows goes on from the kept state."""
+    from grout_b200.kernels import ops
+    from grout_b200.parts.position import scaled_inverse_frequencies
+    H, dk, dv, W = m["heads"], m["dim"], m["vdim"], 24
+    rd = m["rot"]["dims"]
+    w = _ret_weights(m, W, seed=21)
+    wp = torch.cat([w[k] for k in ("q", "k", "v", "g")], 0).double()
+    inv = torch.from_numpy(scaled_inverse_frequencies(rd, m["rot"]["base"], None)).float().to(DEV) if rd else None
+    decay = torch.tensor(m["decay"], dtype=torch.float32, device=DEV)
+    lens = [256, 3, 257, 383, 1, 384, 385, 127, 129, 300]
+    head = [0, 0, 5, 0, 2, 130, 0, 0, 1, 0]                        # rows that an earlier step brought
+    xs = [rnd(h + n + 2, W, seed=50 + i) for i, (h, n) in enumerate(zip(head, lens))]
+    want = [_ret_plain(w, m, x) for x in xs]
+
+    def run(state, seqs, rows, max_rows):
+        step = step_of(seqs)
+        return ops.retention_forward(
+            g32(torch.cat(rows).double() @ wp.T), state, decay, inv, H=H, dk=dk, dv=dv, rot_dim=rd,
+            k_scale=dk ** -0.5, norm_eps=1e-5, token_pos=step.token_pos, cu_q=step.cu_q, slots=step.slots,
+            dtype=torch.float32, max_rows=step.max_q_len if max_rows == "known" else max_rows).float().cpu()
+
+    states = []
+    for max_rows in ("known", None):                               # chunk by chunk, then row by row
+        state = torch.full((len(lens) + 2, H * dk * dv), 7.0, device=DEV)
+        state[1:len(lens) + 1].zero_()
+        with_head = [(i + 1, 0, h) for i, h in enumerate(head) if h]
+        run(state, with_head, [xs[s - 1][:h] for s, _, h in with_head], None)
+        seqs = [(i + 1, h, n) for i, (h, n) in enumerate(zip(head, lens))]
+        rows = [x[h:h + n] for x, h, n in zip(xs, head, lens)]
+        seqs.insert(4, (-1, 0, 260))
+        rows.insert(4, rnd(260, W, seed=49))
+        y = run(state, seqs, rows, max_rows)
+        at = 0
+        for slot, h, n in seqs:
+            if slot > 0:
+                close(y[at:at + n], want[slot - 1][h:h + n], torch.float32, f"{max_rows}: {h} then {n} rows")
+            at += n
+        assert float((state[[0, len(lens) + 1]] - 7.0).abs().max()) == 0.0   # a padding sequence stores nothing
+        states.append(state.clone())
+        y = run(state, [(i + 1, h + n, 2) for i, (h, n) in enumerate(zip(head, lens))],
+                [x[h + n:] for x, h, n in zip(xs, head, lens)], "known")
+        for i, (h, n) in enumerate(zip(head, lens)):
+            close(y[2 * i:2 * i + 2], want[i][h + n:], torch.float32, f"{max_rows}: after {h} and {n} rows")
+    close(states[0], states[1], torch.float32, "kept states")
