@@ -16,7 +16,8 @@
 // sums, stores the cache row and writes the queries' two parts; the rotation
 // pairs element 2i with element 2i + 1.  `heads_mm` is the per-head product
 // out[t, h, :] = W_h x[t, h, :] that folds Wuk into the queries and expands the
-// attention's output, the latter with the gate sigmoid(g) applied to its 32-bit sums.
+// attention's output, the latter with the gate sigmoid(g) applied to its 32-bit sums:
+// for 32-bit tensors a plain tiled kernel, for bfloat16 on the tensor cores.
 #include "common.cuh"
 
 struct LatentArgs {
@@ -162,12 +163,137 @@ __global__ void __launch_bounds__(256) heads_mm_kernel(const HeadsMmArgs a) {
   }
 }
 
+// The same product for bfloat16 on the tensor cores (mma.sync m16n8k16, 32-bit sums).
+// A block owns 32 MW rows and HT_BN columns of one head; its warps stand MW by 2, each
+// with 32 rows and 32 columns: two row tiles by four column tiles of the instruction.
+// x and w both have a head's elements side by side, which is the order the instruction
+// wants its operands in, so a lane reads its pairs from the staged tiles as they are.
+// Rows and elements outside the matrices are staged as zeros.  A sum's order does not
+// depend on T.
+#define HT_BN 64
+#define HT_BK 64
+#define HT_LD (HT_BK + 8)     // 36 words a row: the eight rows a lane group reads fall on different banks
+
+__device__ __forceinline__ void ht_stage(bf16 (*dst)[HT_LD], const bf16* src, size_t ld, int rows_here,
+                                         int k0, int K, int n_rows, bool vec, int tid, int threads) {
+  // n_rows rows of HT_BK elements, eight elements (16 bytes) a turn
+  for (int i = tid; i < n_rows * (HT_BK / 8); i += threads) {
+    const int r = i / (HT_BK / 8), kv = (i % (HT_BK / 8)) * 8;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r < rows_here) {
+      const bf16* p = src + (size_t)r * ld + k0 + kv;
+      if (vec && k0 + kv + 8 <= K) {
+        v = *reinterpret_cast<const uint4*>(p);
+      } else {
+        __align__(16) bf16 e[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) e[j] = k0 + kv + j < K ? p[j] : __float2bfloat16_rn(0.f);
+        v = *reinterpret_cast<const uint4*>(e);
+      }
+    }
+    *reinterpret_cast<uint4*>(&dst[r][kv]) = v;
+  }
+}
+
+template <int MW>
+__global__ void __launch_bounds__(MW * 64) heads_mm_tc_kernel(const HeadsMmArgs a, const int vec) {
+  constexpr int BM = 32 * MW, THREADS = MW * 64;
+  __shared__ __align__(16) bf16 As[BM][HT_LD];
+  __shared__ __align__(16) bf16 Bs[HT_BN][HT_LD];
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, h = blockIdx.z;
+  const int wm = warp >> 1, wn = warp & 1, g = lane >> 2, tig = lane & 3;
+  const int t0 = blockIdx.x * BM, n0 = blockIdx.y * HT_BN;
+  const int K = a.K, N = a.N;
+  const bf16* x = (const bf16*)a.x + ((size_t)t0 * a.H + h) * a.ldx;
+  const bf16* w = (const bf16*)a.w + ((size_t)h * N + n0) * K;
+  float acc[2][4][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += HT_BK) {
+    if (k0) __syncthreads();
+    ht_stage(As, x, (size_t)a.H * a.ldx, min(BM, a.T - t0), k0, K, BM, vec & 1, tid, THREADS);
+    ht_stage(Bs, w, (size_t)K, min(HT_BN, N - n0), k0, K, HT_BN, vec & 2, tid, THREADS);
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < HT_BK; kk += 16) {
+      if (k0 + kk >= K) break;
+      unsigned af[2][4], bfr[4][2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const bf16* r0 = &As[wm * 32 + i * 16 + g][kk + 2 * tig];
+        af[i][0] = *reinterpret_cast<const unsigned*>(r0);
+        af[i][1] = *reinterpret_cast<const unsigned*>(r0 + 8 * HT_LD);
+        af[i][2] = *reinterpret_cast<const unsigned*>(r0 + 8);
+        af[i][3] = *reinterpret_cast<const unsigned*>(r0 + 8 * HT_LD + 8);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const bf16* r0 = &Bs[wn * 32 + j * 8 + g][kk + 2 * tig];
+        bfr[j][0] = *reinterpret_cast<const unsigned*>(r0);
+        bfr[j][1] = *reinterpret_cast<const unsigned*>(r0 + 8);
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          asm volatile(
+              "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+              "{%0,%1,%2,%3};\n"
+              : "+f"(acc[i][j][0]), "+f"(acc[i][j][1]), "+f"(acc[i][j][2]), "+f"(acc[i][j][3])
+              : "r"(af[i][0]), "r"(af[i][1]), "r"(af[i][2]), "r"(af[i][3]), "r"(bfr[j][0]), "r"(bfr[j][1]));
+    }
+  }
+  pdl_launch_dependents_if_large();
+  const bool pack = vec & 4;
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int t = t0 + wm * 32 + i * 16 + g + half * 8;
+      if (t >= a.T) continue;
+      bf16* o = (bf16*)a.out + ((size_t)t * a.H + h) * a.ldo;
+      const float* gp = a.g ? a.g + (size_t)t * a.ldg + h * N : nullptr;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int n = n0 + wn * 32 + j * 8 + 2 * tig;
+        if (n >= N) continue;
+        float v0 = acc[i][j][half * 2], v1 = acc[i][j][half * 2 + 1];
+        if (gp) {
+          v0 *= 1.0f / (1.0f + expf(-gp[n]));
+          if (n + 1 < N) v1 *= 1.0f / (1.0f + expf(-gp[n + 1]));
+        }
+        if (pack && n + 1 < N) {
+          *reinterpret_cast<__nv_bfloat162*>(o + n) = __floats2bfloat162_rn(v0, v1);
+        } else {
+          o[n] = __float2bfloat16_rn(v0);
+          if (n + 1 < N) o[n + 1] = __float2bfloat16_rn(v1);
+        }
+      }
+    }
+}
+
 template <typename T>
 static int heads_mm(const HeadsMmArgs& a, cudaStream_t s) {
   if (a.T < 0 || a.H <= 0 || a.K <= 0 || a.N <= 0 || a.ldx < a.K || a.ldo < a.N || a.H > 65535)
     return GB_ERR_BAD_ARG;
   if (!a.x || !a.w || !a.out) return GB_ERR_BAD_ARG;
   if (a.T == 0) return 0;
+  if (sizeof(T) == 2) {
+    // bit 0: rows of x can be read 16 bytes at a time; bit 1: rows of w; bit 2: pairs of the result stored as one word
+    const int vec = ((a.ldx % 8 == 0 && (uintptr_t)a.x % 16 == 0) ? 1 : 0) |
+                    ((a.K % 8 == 0 && (uintptr_t)a.w % 16 == 0) ? 2 : 0) |
+                    ((a.ldo % 2 == 0 && (uintptr_t)a.out % 4 == 0) ? 4 : 0);
+    const unsigned ny = (a.N + HT_BN - 1) / HT_BN;
+    if (a.T <= 32) return gb_launch(heads_mm_tc_kernel<1>, dim3(1, ny, a.H), dim3(64), 0, s, a, vec);
+    if (a.T <= 64) return gb_launch(heads_mm_tc_kernel<2>, dim3(1, ny, a.H), dim3(128), 0, s, a, vec);
+    return gb_launch(heads_mm_tc_kernel<4>, dim3((a.T + 127) / 128, ny, a.H), dim3(256), 0, s, a, vec);
+  }
   return gb_launch(heads_mm_kernel<T>, dim3((a.T + HM_BM - 1) / HM_BM, (a.N + HM_BN - 1) / HM_BN, a.H),
                    dim3(256), 0, s, a);
 }
