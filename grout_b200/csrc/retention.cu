@@ -210,12 +210,19 @@ __global__ void __launch_bounds__(256) retention_prefix_kernel(const RetentionAr
   const float whole = powf(decay, (float)RT_CHUNK);
   float S = sp ? sp[e] : 0.f;
   const int nz = (n + RT_CHUNK - 1) / RT_CHUNK;
-  for (int z = 0; z < nz; ++z) {
-    float* p = a.chunk_state + (rt_entry(first, z, seq) * H + h) * per + e;
-    const float add = *p;
-    *p = S;
-    const int len = min(RT_CHUNK, n - z * RT_CHUNK);
-    S = fmaf(len == RT_CHUNK ? whole : powf(decay, (float)len), S, add);
+  const float last = powf(decay, (float)(n - (nz - 1) * RT_CHUNK));
+  // eight chunks a turn: their loads are all asked for before the first is used
+  for (int z0 = 0; z0 < nz; z0 += 8) {
+    float add[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      add[j] = z0 + j < nz ? __ldcs(a.chunk_state + (rt_entry(first, z0 + j, seq) * H + h) * per + e) : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (z0 + j >= nz) break;
+      a.chunk_state[(rt_entry(first, z0 + j, seq) * H + h) * per + e] = S;
+      S = fmaf(z0 + j == nz - 1 ? last : whole, S, add[j]);
+    }
   }
   pdl_launch_dependents_if_large();
   if (sp) sp[e] = S;
