@@ -93,10 +93,11 @@ struct TcArgs {
   int transpose_out, out_f32;
   int silu;             // 1 (transposed output only): rows of A are gate|up interleaved in eights,
                         // the output is silu(gate) * up; 3: the same with the tanh form of gelu;
-                        // 2: every output becomes max(x, 0)^2 (a feed-forward without a gate)
+                        // 5: the same with relu; 2: every output becomes max(x, 0)^2 (a feed-forward without a gate)
   int dep_b;            // which operand an earlier kernel writes: 1 = B, 0 = A
   unsigned long long* stamps;   // optional [blocks][8] %globaltimer stamps of the phases, or null
   int split_k;          // > 0: plain split-K, see below
+  const float* bias;    // optional [rowsA], with a gate|up epilogue only: added to the finished sums before the gate
 };
 
 // split_k = S > 0 (transposed 32-bit output only): the grid is tiles x S blocks,
@@ -190,6 +191,7 @@ struct TcConfig {
 // The gate's activation of a gate|up epilogue: silu, g / (1 + e^-g), or (kind 3) the tanh
 // form of gelu, 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))), tanh(x) = 1 - 2 / (e^2x + 1).
 __device__ __forceinline__ float tc_gate_act(float g, int kind) {
+  if (kind == 5) return fmaxf(g, 0.f);   // relu
   if (kind == 3) {
     const float e = __expf(1.5957691216057308f * (g + 0.044715f * g * g * g));
     return 0.5f * g * (2.0f - __fdividef(2.0f, e + 1.0f));
@@ -522,6 +524,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
               }
             }
+          }
+          if (a.bias && (a.silu & 1)) {   // a gate's or an up's bias, by the row of A
+            const float b = row_a < a.rowsA ? a.bias[row_a] : 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) f[j] += b;
           }
           if (a.silu == 2) {   // the finished sums, squared in 32-bit before the one rounding
 #pragma unroll
@@ -893,7 +900,8 @@ GB_EXPORT int gb_gemm_tc_bf16(const void* A, const void* B, const TcArgs* args, 
   if (!A || !B || !args->out || !args->scratch || !args->counters || !args->error) return GB_ERR_BAD_ARG;
   if ((((uintptr_t)A) | ((uintptr_t)B)) & 15) return GB_ERR_BAD_ARG;
   if ((args->silu & 1) && (!args->transpose_out || (args->rowsA % 16))) return GB_ERR_UNSUPPORTED;
-  if (args->silu < 0 || args->silu > 3) return GB_ERR_BAD_ARG;
+  if (args->silu < 0 || args->silu == 4 || args->silu > 5) return GB_ERR_BAD_ARG;
+  if (args->bias && !(args->silu & 1)) return GB_ERR_BAD_ARG;
   TcPlan pl;
   e = tc_plan(args->rowsA, args->rowsB, args->K, &pl);
   if (e) return e;

@@ -47,9 +47,10 @@ struct Tc2Args {
   int* error;    // device int, 0 while all is well
   int M, N, K, ld;
   int out_f32;
-  int silu;      // 1: columns of W^T are gate|up interleaved in eights; out is [M, N / 2]; 3: the same with gelu (tanh form)
-                 // 2: every output becomes max(x, 0)^2 (a feed-forward without a gate)
+  int silu;      // 1: columns of W^T are gate|up interleaved in eights; out is [M, N / 2]; 3: the same with gelu (tanh form);
+                 // 5: the same with relu; 2: every output becomes max(x, 0)^2 (a feed-forward without a gate)
   int bn;        // columns of C per tile: a multiple of 16, 32..256 (filled in by the launcher)
+  const float* bias;   // optional [N], with a gate|up epilogue only: added to the 32-bit sums before the gate
 };
 
 static constexpr int T2_A_BYTES = T2_BM * T2_BK * 2;
@@ -104,8 +105,9 @@ __device__ __forceinline__ void tc_commit_pair(void* bar) {
       : "memory");
 }
 
-// silu, or (kind 3) the tanh form of gelu with tanh(x) = 1 - 2 / (e^2x + 1)
+// silu, (kind 3) the tanh form of gelu with tanh(x) = 1 - 2 / (e^2x + 1), or (kind 5) relu
 __device__ __forceinline__ float t2_gate(float g, int kind) {
+  if (kind == 5) return fmaxf(g, 0.f);
   if (kind == 3) {
     const float e = __expf(1.5957691216057308f * (g + 0.044715f * g * g * g));
     return 0.5f * g * (2.0f - __fdividef(2.0f, e + 1.0f));
@@ -266,6 +268,16 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         }
         if (a.silu & 1) {
           uint32_t w[4];
+          if (a.bias) {
+#pragma unroll
+            for (int c = 0; c < 16; c += 4) {
+              const float4 b = *reinterpret_cast<const float4*>(a.bias + col + c);
+              v[c] = __float_as_uint(__uint_as_float(v[c]) + b.x);
+              v[c + 1] = __float_as_uint(__uint_as_float(v[c + 1]) + b.y);
+              v[c + 2] = __float_as_uint(__uint_as_float(v[c + 2]) + b.z);
+              v[c + 3] = __float_as_uint(__uint_as_float(v[c + 3]) + b.w);
+            }
+          }
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const float g0 = __uint_as_float(v[2 * i]), g1 = __uint_as_float(v[2 * i + 1]);
@@ -337,7 +349,8 @@ GB_EXPORT int gb_gemm_tc2_bf16(const void* X, const void* W, const Tc2Args* args
   if (a.K % 8) return GB_ERR_UNSUPPORTED;
   if ((((uintptr_t)X) | ((uintptr_t)W) | ((uintptr_t)a.out)) & 15) return GB_ERR_BAD_ARG;
   if ((a.silu & 1) && (a.N % 16 || a.out_f32)) return GB_ERR_UNSUPPORTED;
-  if (a.silu < 0 || a.silu > 3) return GB_ERR_BAD_ARG;
+  if (a.silu < 0 || a.silu == 4 || a.silu > 5) return GB_ERR_BAD_ARG;
+  if (a.bias && (!(a.silu & 1) || ((uintptr_t)a.bias & 15))) return GB_ERR_BAD_ARG;
   if ((a.ld * (a.out_f32 ? 4 : 2)) % 16) return GB_ERR_UNSUPPORTED;
   static int sms = 0;
   static bool configured = false;

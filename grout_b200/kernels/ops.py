@@ -841,7 +841,23 @@ def gemm_skinny_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
 class _TcArgs(ctypes.Structure):
     _fields_ = [("out", _P), ("scratch", _P), ("counters", _P), ("error", _P), ("rowsA", _I),
                 ("rowsB", _I), ("K", _I), ("ld", _I), ("transpose_out", _I), ("out_f32", _I),
-                ("silu", _I), ("dep_b", _I), ("stamps", _P), ("split_k", _I)]
+                ("silu", _I), ("dep_b", _I), ("stamps", _P), ("split_k", _I), ("bias", _P)]
+
+
+_GATE_CODES = {"silu": 1, "gelu_tanh": 3, "relu": 5}     # the products' codes of a gate|up epilogue
+
+
+def _gate_code(gate_act: str, bias, silu_mul: bool, n_fused: int):
+    """The epilogue's code and the bias it adds first (32-bit, one entry per fused row)."""
+    if gate_act not in _GATE_CODES:
+        raise KernelError(f"gate activation '{gate_act}': one of {sorted(_GATE_CODES)}")
+    if bias is not None:
+        if not silu_mul:
+            raise KernelError("a bias goes with the gate|up epilogue")
+        _need(bias, "gate|up bias", torch.float32, 1)
+        if bias.shape[0] != n_fused:
+            raise KernelError(f"the gate|up bias has {bias.shape[0]} entries for {n_fused} fused rows")
+    return _GATE_CODES[gate_act]
 
 
 _TC_PLANS = {}
@@ -893,7 +909,8 @@ def tc_wait_selftest(device, limit_us: int = 1000) -> int:
 def gemm_tc_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
                  swap: Optional[bool] = None, silu_mul: bool = False,
                  stamps: Optional[torch.Tensor] = None, split_out: bool = False,
-                 relu_squared: bool = False, gate_act: str = "silu") -> torch.Tensor:
+                 relu_squared: bool = False, gate_act: str = "silu",
+                 bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x [M, K] . w [N, K]^T on the tcgen05 tensor cores (TMA-fed, accumulator in
     tensor memory).  ``swap``: put the weight rows on the 128-row side of the MMA
     and the activation rows on the narrow side (the layout for few rows); by
@@ -905,9 +922,10 @@ def gemm_tc_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
     preparation does so in the kernel it runs anyway); otherwise the result is the
     ordinary [M, N].  ``relu_squared``: every output becomes max(y, 0)^2, squared in
     32-bit before the rounding (not with ``silu_mul`` or ``split_out``).  ``gate_act``
-    (with ``silu_mul``): "silu" or "gelu_tanh", the activation the gate passes through."""
-    if gate_act not in ("silu", "gelu_tanh"):
-        raise KernelError(f"gate activation '{gate_act}': 'silu' or 'gelu_tanh'")
+    (with ``silu_mul``): "silu", "gelu_tanh" or "relu", the activation the gate passes
+    through; ``bias`` (with ``silu_mul``) [N] 32-bit in the order of ``w``'s rows: added to
+    the 32-bit sums of gate and up before the activation."""
+    gate_code = _gate_code(gate_act, bias, silu_mul, w.shape[0])
     _need(x, "activations", torch.bfloat16, 2)
     _need(w, "weight", torch.bfloat16, 2)
     M, K = x.shape
@@ -947,7 +965,8 @@ def gemm_tc_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
         a.rowsA, a.rowsB, a.K, a.ld = A.shape[0], B.shape[0], K, n_out
         a.transpose_out, a.out_f32 = int(swap), int(out_dtype == torch.float32 or bool(split))
         a.split_k = split
-        a.silu = 2 if relu_squared else ((3 if gate_act == "gelu_tanh" else 1) if silu_mul else 0)
+        a.silu = 2 if relu_squared else (gate_code if silu_mul else 0)
+        a.bias = _ptr(bias)
         a.dep_b = int(swap)                             # the activations are another kernel's output
         a.stamps = _ptr(stamps)     # int64 [blocks, 8]: phase times of every block, for tuning
         _check(_fn("gemm_tc", "gb_gemm_tc_bf16", "pppp")(
@@ -959,7 +978,7 @@ def gemm_tc_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
 
 class _Tc2Args(ctypes.Structure):
     _fields_ = [("out", _P), ("error", _P), ("M", _I), ("N", _I), ("K", _I), ("ld", _I),
-                ("out_f32", _I), ("silu", _I), ("bn", _I)]
+                ("out_f32", _I), ("silu", _I), ("bn", _I), ("bias", _P)]
 
 
 _TC_ERROR_NAMES.update({121: "the pair product's MMA lane waited 2 s for a stage that never arrived",
@@ -994,15 +1013,16 @@ def gemm_tc2_pays(M: int, N: int, device, fused_silu: bool) -> bool:
 @_profiled("gemm_tc2_bf16", _cost_gemm)
 def gemm_tc2_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
                   silu_mul: bool = False, tile_cols: int = 0,
-                  relu_squared: bool = False, gate_act: str = "silu") -> torch.Tensor:
+                  relu_squared: bool = False, gate_act: str = "silu",
+                  bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x [M, K] . w [N, K]^T for many rows on pairs of SMs (tcgen05.mma.cta_group::2,
     tiles of 256 rows and ``tile_cols`` columns: a multiple of 16 up to 256, by
     default chosen by the kernel's launcher for the shape).  ``silu_mul``: the rows of ``w`` are gate and up rows
     interleaved in groups of 8 and the result is silu(gate) * up, [M, N / 2].
     ``relu_squared`` (instead): every output becomes max(y, 0)^2, squared in 32-bit.
-    ``gate_act`` (with ``silu_mul``): "silu" or "gelu_tanh"."""
-    if gate_act not in ("silu", "gelu_tanh"):
-        raise KernelError(f"gate activation '{gate_act}': 'silu' or 'gelu_tanh'")
+    ``gate_act`` (with ``silu_mul``): "silu", "gelu_tanh" or "relu"; ``bias`` (with
+    ``silu_mul``) [N] 32-bit in the order of ``w``'s rows, added to the sums before the gate."""
+    gate_code = _gate_code(gate_act, bias, silu_mul, w.shape[0])
     _need(x, "activations", torch.bfloat16, 2)
     _need(w, "weight", torch.bfloat16, 2)
     M, K = x.shape
@@ -1027,7 +1047,8 @@ def gemm_tc2_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
     a.out, a.error = y.data_ptr(), _tc_error_flag(x.device).data_ptr()
     a.M, a.N, a.K, a.ld = M, N, K, n_out
     a.out_f32, a.bn = int(out_dtype == torch.float32), int(tile_cols)
-    a.silu = 2 if relu_squared else ((3 if gate_act == "gelu_tanh" else 1) if silu_mul else 0)
+    a.silu = 2 if relu_squared else (gate_code if silu_mul else 0)
+    a.bias = _ptr(bias)
     with torch.cuda.device(x.device):
         _check(_fn("gemm_tc2", "gb_gemm_tc2_bf16", "pppp")(
             x.data_ptr(), w.data_ptr(), ctypes.addressof(a), _stream()), "gemm_tc2_bf16")

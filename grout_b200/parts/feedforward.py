@@ -166,16 +166,13 @@ class GatedMLP(FeedForward):
 
     def forward(self, x, step):
         if self.has_bias:
-            sums = self.gate_up(x, out_dtype=torch.float32)
-            inner = ops.bias_gate_mul(sums, self.gate_up_bias, self.activation, self.ctx.dtype,
-                                      self.interleave)
+            # the biases join the product's 32-bit sums: in its epilogue where it has one
+            inner = self.gate_up.silu_mul(x, self.interleave, self.activation, bias=self.gate_up_bias)
             d = self.down(inner, out_dtype=torch.float32, partial_ok=True)
             # partial sums: the bias joins the first; else one 32-bit term for the norm to add
             d = d if d.dim() == 3 else d.unsqueeze(0)
             ops.add_bias_(d[0], self.down_bias)
             return d
-        if self.activation == "relu":
-            return self.down(ops.relu_mul(self.gate_up(x), self.interleave), partial_ok=True)
         return self.down(self.gate_up.silu_mul(x, self.interleave, self.activation), partial_ok=True)
 
 

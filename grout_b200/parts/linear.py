@@ -84,14 +84,15 @@ class Linear:
                 return ops.gemm_tc2_bf16(x, w, out_dtype)
         return ops.library_mm(x, w, out_dtype)
 
-    def silu_mul(self, x: torch.Tensor, interleave: int, activation: str = "silu") -> torch.Tensor:
-        """act(gate) * up of a fused gate|up weight, ``activation`` "silu" or
-        "gelu_tanh".  ``interleave`` 0: gate rows first, then up rows; 8: groups of 8
+    def silu_mul(self, x: torch.Tensor, interleave: int, activation: str = "silu",
+                 bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """act(gate + bg) * (up + bu) of a fused gate|up weight, ``activation`` "silu",
+        "gelu_tanh" or "relu", ``bias`` the fused [bg | bu] in the rows' order or None.  ``interleave`` 0: gate rows first, then up rows; 8: groups of 8
         gate rows followed by their 8 up rows, which lets the tcgen05 kernels finish
         the product in their epilogue."""
         w = self.weight
-        if activation != "silu":
-            return self._gated(x, interleave, activation)
+        if activation != "silu" or bias is not None:
+            return self._gated(x, interleave, activation, bias)
         if (interleave == 8 and w.dtype == torch.bfloat16 and x.shape[0] <= ops.SKINNY_MAX_ROWS
                 and self.in_features % 8 == 0):
             if self.decode_kernel == "tc":
@@ -105,21 +106,28 @@ class Linear:
             return ops.gemm_tc2_bf16(x, w, x.dtype, silu_mul=True)
         return ops.silu_mul(self(x), interleave)
 
-    def _gated(self, x: torch.Tensor, interleave: int, activation: str) -> torch.Tensor:
-        """The gate|up product with another activation than silu: the tcgen05 kernels
-        have it as an epilogue (the mma.sync decode kernel has not), under the rules of
-        ``silu_mul``; elsewhere the product and an elementwise kernel."""
+    def _gated(self, x: torch.Tensor, interleave: int, activation: str,
+               bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The gate|up product with another activation than silu ("gelu_tanh", "relu") or
+        with a ``bias`` (32-bit, in the fused rows' order, added to the 32-bit sums before
+        the gate): the tcgen05 kernels have it as an epilogue (the mma.sync decode kernel
+        has not), under the rules of ``silu_mul``; elsewhere the product and an
+        elementwise kernel."""
         w = self.weight
         fusable = (interleave == 8 and w.dtype == torch.bfloat16 and x.dtype == torch.bfloat16
                    and self.in_features % 8 == 0)
         if fusable and x.shape[0] <= ops.SKINNY_MAX_ROWS and self.decode_kernel == "tc":
-            return ops.gemm_tc_bf16(x, w, x.dtype, swap=True, silu_mul=True, gate_act=activation)
+            return ops.gemm_tc_bf16(x, w, x.dtype, swap=True, silu_mul=True, gate_act=activation, bias=bias)
         if (fusable and x.shape[0] > ops.SKINNY_MAX_ROWS and self.out_features % 32 == 0
                 and (self.prefill_kernel == "pair" or
                      (self.prefill_kernel == "auto" and
                       ops.gemm_tc2_pays(x.shape[0], self.out_features, x.device, fused_silu=True)))):
-            return ops.gemm_tc2_bf16(x, w, x.dtype, silu_mul=True, gate_act=activation)
+            return ops.gemm_tc2_bf16(x, w, x.dtype, silu_mul=True, gate_act=activation, bias=bias)
+        if bias is not None:
+            return ops.bias_gate_mul(self(x, out_dtype=torch.float32), bias, activation, x.dtype, interleave)
         y = self(x)
+        if activation == "relu":
+            return ops.relu_mul(y, interleave)
         return ops.gelu_tanh_mul(y, interleave) if activation == "gelu_tanh" else ops.silu_mul(y, interleave)
 
     def relu_squared(self, x: torch.Tensor) -> torch.Tensor:

@@ -510,3 +510,27 @@ def test_retention_long_sequences_go_chunk_by_chunk(m):
         for i, (h, n) in enumerate(zip(head, lens)):
             close(y[2 * i:2 * i + 2], want[i][h + n:], torch.float32, f"{max_rows}: after {h} and {n} rows")
     close(states[0], states[1], torch.float32, "kept states")
+
+
+@pytest.mark.parametrize("act", ["relu", "silu", "gelu_tanh"])
+@pytest.mark.parametrize("rows,F,W", [(5, 48, 64), (64, 96, 40), (300, 160, 72), (513, 32, 256)])
+def test_gate_epilogue_with_biases_of_the_tensor_core_products(act, rows, F, W):
+    """act(x Wg^T + bg) * (x Wu^T + bu) as the epilogue of the product for few rows and of
+    the product for many, against the same in double precision from the same bfloat16
+    operands; a bias large enough that leaving it out, or adding it behind the gate, shows."""
+    from grout_b200.kernels import ops
+    g, u = rnd(F, W, seed=1, scale=0.3).bfloat16(), rnd(F, W, seed=2, scale=0.3).bfloat16()
+    bg, bu = rnd(F, seed=3, scale=1.5), rnd(F, seed=4, scale=1.5)
+    x = rnd(rows, W, seed=5).bfloat16()
+    fused = torch.stack([g.view(-1, 8, W), u.view(-1, 8, W)], dim=1).reshape(2 * F, W).contiguous().to(DEV)
+    bias = torch.stack([bg.view(-1, 8), bu.view(-1, 8)], dim=1).reshape(-1).contiguous().to(DEV)
+    zg, zu = x.double() @ g.double().T + bg.double(), x.double() @ u.double().T + bu.double()
+    fn = {"relu": torch.relu, "silu": torch.nn.functional.silu,
+          "gelu_tanh": lambda z: torch.nn.functional.gelu(z, approximate="tanh")}[act]
+    want = fn(zg) * zu
+    assert float((want - fn(zg - bg.double()) * (zu - bu.double())).abs().max()) > 1.0
+    got = [ops.gemm_tc2_bf16(x.to(DEV), fused, torch.bfloat16, silu_mul=True, gate_act=act, bias=bias)]
+    if rows <= ops.SKINNY_MAX_ROWS:
+        got.append(ops.gemm_tc_bf16(x.to(DEV), fused, torch.bfloat16, swap=True, silu_mul=True, gate_act=act, bias=bias))
+    for y in got:
+        close(y.float(), want, torch.bfloat16, f"{act} {rows}x{F}x{W}")
