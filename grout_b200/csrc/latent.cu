@@ -35,54 +35,62 @@ struct LatentArgs {
   float eps;
 };
 
+// A block owns one token and the heads blockIdx.y * heads_per_block ..; the block of the
+// first heads also normalises the latent and stores the token's cache row.
 template <typename T>
-__global__ void __launch_bounds__(256) latent_prepare_kernel(const LatentArgs a) {
+__global__ void __launch_bounds__(256) latent_prepare_kernel(const LatentArgs a, const int heads_per_block) {
   __shared__ float scratch[32];
   pdl_launch_dependents_if_small();
   pdl_wait();
   const int t = blockIdx.x, tid = threadIdx.x;
   const int H = a.H, dn = a.dn, dr = a.dr, R = a.R, Ds = a.Ds;
+  const int h0 = blockIdx.y * heads_per_block, nh = min(heads_per_block, H - h0);
   const int C = H * (dn + dr) + R + dr + H * a.dv;
-  const float* row = a.proj + (size_t)t * C;
-  const float* down = row + H * (dn + dr);
+  const float* __restrict__ row = a.proj + (size_t)t * C;
+  const float* __restrict__ down = row + H * (dn + dr);
   const float pos = (float)a.token_pos[t];
-  float ss = 0.f;
-  for (int i = tid; i < R; i += blockDim.x) ss = fmaf(down[i], down[i], ss);
-  const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)R + a.eps);
-  pdl_launch_dependents_if_large();
-  const int slot = a.slots[a.token_seq[t]];
-  if (slot >= 0) {
-    const int p = a.token_pos[t];
-    const int pg = a.block_table[(size_t)slot * a.max_pages + p / a.page];
-    T* dst = (T*)a.pages + ((size_t)pg * a.page + p % a.page) * Ds;
-    for (int i = tid; i < Ds; i += blockDim.x) {
-      float v = 0.f;
-      if (i < R) v = down[i] * inv * a.norm_w[i];
-      else if (i < R + dr) {
-        const int e = i - R, pair = e >> 1;
-        float s, c;
-        sincosf(pos * a.inv_freq[pair], &s, &c);
-        const float u = down[R + 2 * pair], w = down[R + 2 * pair + 1];
-        v = (e & 1) ? w * c + u * s : u * c - w * s;
+  if (blockIdx.y == 0) {
+    float ss = 0.f;
+    for (int i = tid; i < R; i += blockDim.x) ss = fmaf(down[i], down[i], ss);
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)R + a.eps);
+    const int slot = a.slots[a.token_seq[t]];
+    if (slot >= 0) {
+      const int p = a.token_pos[t];
+      const int pg = a.block_table[(size_t)slot * a.max_pages + p / a.page];
+      T* dst = (T*)a.pages + ((size_t)pg * a.page + p % a.page) * Ds;
+      for (int i = tid; i < Ds; i += blockDim.x) {
+        float v = 0.f;
+        if (i < R) v = down[i] * inv * a.norm_w[i];
+        else if (i < R + dr) {
+          const int e = i - R, pair = e >> 1;
+          float s, c;
+          sincosf(pos * a.inv_freq[pair], &s, &c);
+          const float u = down[R + 2 * pair], w = down[R + 2 * pair + 1];
+          v = (e & 1) ? w * c + u * s : u * c - w * s;
+        }
+        dst[i] = from_f32<T>(v);
       }
-      dst[i] = from_f32<T>(v);
     }
   }
-  for (int i = tid; i < H * (dn + dr); i += blockDim.x) {
+  pdl_launch_dependents_if_large();
+  T* __restrict__ q_plain = (T*)a.q_plain + ((size_t)t * H + h0) * dn;
+  T* __restrict__ q_full = (T*)a.q_full + ((size_t)t * H + h0) * Ds;
+  const float* __restrict__ qrow = row + (size_t)h0 * (dn + dr);
+  for (int i = tid; i < nh * (dn + dr); i += blockDim.x) {
     const int h = i / (dn + dr), e = i % (dn + dr);
     if (e < dn) {
-      ((T*)a.q_plain)[((size_t)t * H + h) * dn + e] = from_f32<T>(row[i]);
+      q_plain[(size_t)h * dn + e] = from_f32<T>(qrow[i]);
     } else {
       const int r = e - dn, pair = r >> 1;
       float s, c;
       sincosf(pos * a.inv_freq[pair], &s, &c);
-      const float u = row[h * (dn + dr) + dn + 2 * pair], w = row[h * (dn + dr) + dn + 2 * pair + 1];
-      ((T*)a.q_full)[((size_t)t * H + h) * Ds + R + r] = from_f32<T>((r & 1) ? w * c + u * s : u * c - w * s);
+      const float u = qrow[h * (dn + dr) + dn + 2 * pair], w = qrow[h * (dn + dr) + dn + 2 * pair + 1];
+      q_full[(size_t)h * Ds + R + r] = from_f32<T>((r & 1) ? w * c + u * s : u * c - w * s);
     }
   }
-  for (int i = tid; i < H * (Ds - R - dr); i += blockDim.x) {
+  for (int i = tid; i < nh * (Ds - R - dr); i += blockDim.x) {
     const int h = i / (Ds - R - dr), e = i % (Ds - R - dr);
-    ((T*)a.q_full)[((size_t)t * H + h) * Ds + R + dr + e] = from_f32<T>(0.f);
+    q_full[(size_t)h * Ds + R + dr + e] = from_f32<T>(0.f);
   }
 }
 
@@ -95,7 +103,10 @@ static int latent_prepare(const LatentArgs& a, cudaStream_t s) {
       !a.q_plain || !a.q_full || (a.dr && !a.inv_freq))
     return GB_ERR_BAD_ARG;
   if (a.n_tokens == 0) return 0;
-  return gb_launch(latent_prepare_kernel<T>, dim3(a.n_tokens), dim3(256), 0, s, a);
+  // few tokens: four heads a block, so that a step of a handful of rows fills more than a handful of SMs
+  const int heads_per_block = a.n_tokens <= 64 ? min(a.H, 4) : a.H;
+  return gb_launch(latent_prepare_kernel<T>, dim3(a.n_tokens, (a.H + heads_per_block - 1) / heads_per_block),
+                   dim3(256), 0, s, a, heads_per_block);
 }
 GB_EXPORT int gb_latent_prepare_f32(const LatentArgs* a, cudaStream_t s) { return latent_prepare<float>(*a, s); }
 GB_EXPORT int gb_latent_prepare_bf16(const LatentArgs* a, cudaStream_t s) { return latent_prepare<bf16>(*a, s); }
@@ -174,24 +185,33 @@ __global__ void __launch_bounds__(256) heads_mm_kernel(const HeadsMmArgs a) {
 #define HT_BK 64
 #define HT_LD (HT_BK + 8)     // 36 words a row: the eight rows a lane group reads fall on different banks
 
+// ITERS turns of eight elements (16 bytes) a thread: all of a thread's loads are asked for
+// before the first is stored, so a stage costs one trip to memory, not one a turn.
+template <int ITERS, int THREADS>
 __device__ __forceinline__ void ht_stage(bf16 (*dst)[HT_LD], const bf16* src, size_t ld, int rows_here,
-                                         int k0, int K, int n_rows, bool vec, int tid, int threads) {
-  // n_rows rows of HT_BK elements, eight elements (16 bytes) a turn
-  for (int i = tid; i < n_rows * (HT_BK / 8); i += threads) {
+                                         int k0, int K, bool vec, int tid) {
+  uint4 v[ITERS];
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int i = tid + it * THREADS;
     const int r = i / (HT_BK / 8), kv = (i % (HT_BK / 8)) * 8;
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    v[it] = make_uint4(0u, 0u, 0u, 0u);
     if (r < rows_here) {
       const bf16* p = src + (size_t)r * ld + k0 + kv;
       if (vec && k0 + kv + 8 <= K) {
-        v = *reinterpret_cast<const uint4*>(p);
+        v[it] = *reinterpret_cast<const uint4*>(p);
       } else {
         __align__(16) bf16 e[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) e[j] = k0 + kv + j < K ? p[j] : __float2bfloat16_rn(0.f);
-        v = *reinterpret_cast<const uint4*>(e);
+        v[it] = *reinterpret_cast<const uint4*>(e);
       }
     }
-    *reinterpret_cast<uint4*>(&dst[r][kv]) = v;
+  }
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int i = tid + it * THREADS;
+    *reinterpret_cast<uint4*>(&dst[i / (HT_BK / 8)][(i % (HT_BK / 8)) * 8]) = v[it];
   }
 }
 
@@ -217,8 +237,8 @@ __global__ void __launch_bounds__(MW * 64) heads_mm_tc_kernel(const HeadsMmArgs 
       for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.f;
   for (int k0 = 0; k0 < K; k0 += HT_BK) {
     if (k0) __syncthreads();
-    ht_stage(As, x, (size_t)a.H * a.ldx, min(BM, a.T - t0), k0, K, BM, vec & 1, tid, THREADS);
-    ht_stage(Bs, w, (size_t)K, min(HT_BN, N - n0), k0, K, HT_BN, vec & 2, tid, THREADS);
+    ht_stage<BM * (HT_BK / 8) / THREADS, THREADS>(As, x, (size_t)a.H * a.ldx, min(BM, a.T - t0), k0, K, vec & 1, tid);
+    ht_stage<HT_BN * (HT_BK / 8) / THREADS, THREADS>(Bs, w, (size_t)K, min(HT_BN, N - n0), k0, K, vec & 2, tid);
     __syncthreads();
 #pragma unroll
     for (int kk = 0; kk < HT_BK; kk += 16) {
