@@ -1502,6 +1502,25 @@ def delta_forward(proj: torch.Tensor, state: torch.Tensor, conv_w: torch.Tensor,
     return y
 
 
+# ---------------------------------------------------------------- groups of heads
+@_profiled("head_group", _cost_io)
+def head_group(x: torch.Tensor, first: int, count: int) -> torch.Tensor:
+    """Heads first .. first + count of x [T, H, D] as a tensor of their own (a copy by the
+    library's kernel; it is here so that the profile and the launch log see it)."""
+    _need(x, "rows per head", ndim=3)
+    out = x[:, first:first + count].contiguous()
+    _check(0, "head_group")
+    return out
+
+
+@_profiled("join_heads", _cost_io)
+def join_heads(parts) -> torch.Tensor:
+    """Tensors [T, h_i, D] side by side along the heads (the library's kernel, logged)."""
+    out = torch.cat(list(parts), dim=1)
+    _check(0, "join_heads")
+    return out
+
+
 # ---------------------------------------------------------------- retention
 class _RetentionArgs(ctypes.Structure):
     _fields_ = [("proj", _P), ("decay", _P), ("inv_freq", _P), ("token_pos", _P), ("cu_q", _P),

@@ -308,9 +308,9 @@ class LatentAttention(Mixer):
         if (self.H <= self.GROUP or q.dtype != torch.bfloat16
                 or not ops.fast_attention_takes(self.Ds, self.GROUP, 1, cache.page)):
             return ops.attention(q, cache.k_pages, cache.v_pages, cache.block_table, **kw)
-        return torch.cat([ops.attention(q[:, a:a + self.GROUP].contiguous(), cache.k_pages, cache.v_pages,
-                                        cache.block_table, **kw)
-                          for a in range(0, self.H, self.GROUP)], dim=1)
+        return ops.join_heads([ops.attention(ops.head_group(q, a, min(self.GROUP, self.H - a)), cache.k_pages,
+                                             cache.v_pages, cache.block_table, **kw)
+                               for a in range(0, self.H, self.GROUP)])
 
     def captures_prompts(self):
         return True
