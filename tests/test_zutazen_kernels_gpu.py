@@ -534,3 +534,80 @@ def test_gate_epilogue_with_biases_of_the_tensor_core_products(act, rows, F, W):
         got.append(ops.gemm_tc_bf16(x.to(DEV), fused, torch.bfloat16, swap=True, silu_mul=True, gate_act=act, bias=bias))
     for y in got:
         close(y.float(), want, torch.bfloat16, f"{act} {rows}x{F}x{W}")
+
+
+# ------------------------------------------------------------------ latent attention, through its part
+def _lat_weights(m, W, seed, sharp):
+    g = torch.Generator().manual_seed(seed)
+    r = lambda *s, sc=1.0: torch.randn(*s, generator=g) * sc
+    H, dn, dr, dv, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+    return {"q": r(H * (dn + dr), W, sc=sharp / math.sqrt(W)), "dkv": r(R + dr, W, sc=1 / math.sqrt(W)),
+            "dkv.norm": 1 + r(R, sc=0.2), "uk": r(H * dn, R, sc=sharp / math.sqrt(R)),
+            "uv": r(H * dv, R, sc=1 / math.sqrt(R)), "g": r(H * dv, W, sc=1 / math.sqrt(W)),
+            "o": r(W, H * dv, sc=1 / math.sqrt(H * dv))}
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(3, 16, 8, 16, 24, 64), (20, 32, 16, 32, 48, 65), (2, 24, 0, 40, 40, 5),
+                                   (17, 64, 32, 64, 96, 130), (1, 8, 4, 8, 300, 63)])
+def test_latent_attention_windows_pages_and_cuts(dtype, shape):
+    """Through the mixer part and a paged cache: windows of a page, of one more and of one
+    less, and longer than two pages, passing over a prompt and over decoded tokens; the same
+    rows in other cuts; the scores are sharp enough that a window one token off, in either
+    direction, would show in the rows behind the window."""
+    from grout_b200.cache import CacheLayout, SequenceCache
+    from grout_b200.parts import BuildContext, PartSpec, build_part
+    H, dn, dr, dv, R, window = shape
+    W, T, eps = 48, 210, 1e-5
+    m = dict(heads=H, dim=dn, rot_dim=dr, vdim=dv, kv_rank=R, scale=(dn + dr) ** -0.5,
+             rot={"base": 1e4, "dims": dr}, mask={"size": window})
+    w = {k: v.to(dtype) for k, v in _lat_weights(m, W, seed=31, sharp=4.0).items()}
+    x = rnd(T, W, seed=32).to(dtype)
+    pw = {"m." + k: v for k, v in w.items()}
+    want = plain.latent_attention_mixer(x, pw, "m.", m, eps)
+    for other in (window - 1, window + 1):
+        if other > 0:
+            off = plain.latent_attention_mixer(x, pw, "m.", dict(m, mask={"size": other}), eps)
+            assert float((off - want)[window:].abs().max()) > 0.1 * float(want.abs().max())
+            assert float((off - want)[:min(window, other) - 1].abs().max()) < 1e-9 if min(window, other) > 1 else True
+    position = (PartSpec("rotary_interleaved", dict(head_dim=dr, theta=1e4, rot_dim=dr, exact_table=True))
+                if dr else PartSpec("none", {}))
+    part = build_part("mixer", PartSpec("latent_attention", dict(
+        hidden=W, n_heads=H, head_dim=dn, rot_dim=dr, v_head_dim=dv, kv_rank=R, position=position,
+        scale=m["scale"], norm_eps=eps, window=window, gated=True)), BuildContext(dtype, torch.device(DEV)))
+    part.load({k: v.to(DEV) for k, v in w.items()})
+    cache = SequenceCache(CacheLayout.from_specs([part.cache_spec()]), max_tokens=1024, max_slots=3,
+                          max_seq_len=256, dtype=dtype, device=DEV)
+    first = None
+    for cuts in ([T], [window + 2] + [1] * (T - window - 2) if window + 2 < T else [T - 1, 1],
+                 [63, 2, 64, 1, 70, 1, 1, 8], [2] * (T // 2)):
+        held = cache.open()                                   # another request holds pages in between
+        cache.reserve(held, 70)
+        slot = cache.open()
+        outs, start = [], 0
+        for n in cuts:
+            cache.reserve(slot, n)
+            cache.flush()
+            step = make_step([(slot, start, n)])
+            y = part.forward(x[start:start + n].to(DEV), step, cache.view(0))
+            outs.append((y.sum(0) if y.dim() == 3 else y).float().cpu())
+            cache.advance(slot, n)
+            start += n
+        cache.close(held)
+        cache.close(slot)                                     # the pages serve the next cut
+        got = torch.cat(outs)
+        if dtype == torch.float32:
+            close(got, want, dtype, str(cuts[:4]))
+        else:
+            d = got.double() - want
+            assert float(d.pow(2).mean().sqrt() / want.pow(2).mean().sqrt()) < 0.03, cuts[:4]
+            assert float(d.abs().max()) < 0.15 * float(want.abs().max()), cuts[:4]
+        if first is None:
+            first = got
+        elif dtype == torch.float32:
+            close(got, first, dtype, "cut against whole")
+
+
+def make_step(seqs):
+    from grout_b200.engine.batch import make_context
+    return make_context([(s, st, [0] * n) for s, st, n in seqs], None, DEV)
