@@ -21,11 +21,13 @@
 // applies the gate.
 //
 // A step in which a sequence brings RT_CHUNK_MIN rows or more goes chunk by chunk, five
-// kernels: `scan` walks every chunk of RT_CHUNK rows at the same time, each from zeros,
-// and leaves the chunk's read-outs within itself and what the chunk adds to the state;
-// `prefix` turns those into the states at the chunks' starts (S <- decay^rows S + added,
-// in the chunks' order) and stores the last; `cross` adds decay^(j+1) S_start^T q to row
-// j of every chunk, a tiled 32-bit product.
+// kernels.  `chunk` takes every chunk of RT_CHUNK rows at the same time, each from zeros,
+// as three tiled 32-bit products: P = (Q K^T) under the mask decay^(i-j) (j <= i), the
+// read-outs within the chunk P V, and what the chunk adds to the state,
+// sum_t decay^(rows-1-t) k_t v_t^T.  `prefix` turns those into the states at the chunks'
+// starts (S <- decay^rows S + added, in the chunks' order) and stores the last; `cross`
+// adds decay^(j+1) S_start^T q to row j of every chunk, a tiled 32-bit product too.  The
+// recurrence is linear, so this is the same sum in another order.
 //
 // A step in which every sequence brings one row (decoding) is one kernel, `step`:
 // a block owns one (sequence, head), turns the row's q and k itself, streams the
@@ -44,7 +46,7 @@ struct RetentionArgs {
   long long state_stride;
   float* qk;              // [T, 2, H, dk] scratch: turned q, turned and scaled k
   float* o;               // [T, H, dv] scratch: the read-outs
-  float* chunk_state;     // [T / RT_CHUNK + n_seqs, H, dk, dv] scratch of the chunked scan
+  float* chunk_state;     // [T / RT_CHUNK + n_seqs, H, dk, dv] scratch of a step that goes chunk by chunk
   void* y;                // [T, H dv]
   int n_tokens, n_seqs, H, dk, dv, rot_dim;
   float k_scale, norm_eps;
@@ -54,7 +56,7 @@ struct RetentionArgs {
 #define RT_LANES 8      // lanes that share a column of the state
 #define RT_COLS 16      // columns a block owns
 #define RT_STAGE 16     // rows staged at a time
-#define RT_CHUNK 128    // rows of a chunk where a sequence brings more than that
+#define RT_CHUNK 64     // rows of a chunk where a sequence brings more than that
 #define RT_TM 64        // rows of a block of the chunks' second pass
 #define RT_TN 128       // columns of its tile
 #define RT_TK 16        // elements of a head it stages at a time
@@ -99,9 +101,7 @@ __device__ __forceinline__ size_t rt_entry(int first, int z, int seq) {
   return (size_t)((first + z * RT_CHUNK) / RT_CHUNK + seq);
 }
 
-// CHUNKED: blockIdx.z also counts the sequence's chunks; a block walks one chunk's rows
-// from a state of zeros and leaves what the chunk alone adds up to in the chunk's entry.
-template <int KPL, bool CHUNKED>
+template <int KPL>
 __global__ void __launch_bounds__(RT_COLS* RT_LANES) retention_scan_kernel(const RetentionArgs a) {
   constexpr int DKP = KPL * RT_LANES;            // dk rounded up; the rest is zeros
   __shared__ __align__(16) float qs[RT_STAGE][DKP];
@@ -109,33 +109,20 @@ __global__ void __launch_bounds__(RT_COLS* RT_LANES) retention_scan_kernel(const
   __shared__ float vs[RT_STAGE][RT_COLS];
   pdl_launch_dependents_if_small();
   pdl_wait();
+  const int h = blockIdx.x, seq = blockIdx.y, c0 = blockIdx.z * RT_COLS;
   const int H = a.H, dk = a.dk, dv = a.dv;
-  const int groups = (dv + RT_COLS - 1) / RT_COLS;
-  const int h = blockIdx.x, seq = blockIdx.y;
-  const int z = CHUNKED ? blockIdx.z / groups : 0;
-  const int c0 = (CHUNKED ? blockIdx.z % groups : blockIdx.z) * RT_COLS;
-  int first = a.cu_q[seq], n = a.cu_q[seq + 1] - first;
-  if (CHUNKED) {
-    if (z * RT_CHUNK >= n) return;
-    n = min(RT_CHUNK, n - z * RT_CHUNK);
-  }
+  const int first = a.cu_q[seq], n = a.cu_q[seq + 1] - first;
   if (n <= 0) return;
   const int tid = threadIdx.x, lane = tid % RT_LANES, col = c0 + tid / RT_LANES;
   const bool live = col < dv;
-  float* sp;
-  if (CHUNKED) {
-    sp = a.chunk_state + (rt_entry(first, z, seq) * H + h) * dk * dv;
-    first += z * RT_CHUNK;
-  } else {
-    const int slot = a.slots[seq];
-    sp = slot >= 0 ? a.state + (size_t)slot * a.state_stride + (size_t)h * dk * dv : nullptr;
-  }
+  const int slot = a.slots[seq];
+  float* sp = slot >= 0 ? a.state + (size_t)slot * a.state_stride + (size_t)h * dk * dv : nullptr;
   const float decay = a.decay[h];
   float S[KPL];
 #pragma unroll
   for (int r = 0; r < KPL; ++r) {
     const int i = rt_row<KPL>(lane, r);
-    S[r] = (!CHUNKED && sp && live && i < dk) ? sp[(size_t)i * dv + col] : 0.f;
+    S[r] = (sp && live && i < dk) ? sp[(size_t)i * dv + col] : 0.f;
   }
   const int C = 2 * H * dk + 2 * H * dv;
   for (int t0 = 0; t0 < n; t0 += RT_STAGE) {
@@ -191,6 +178,138 @@ __global__ void __launch_bounds__(RT_COLS* RT_LANES) retention_scan_kernel(const
       if (i < dk) sp[(size_t)i * dv + col] = S[r];
     }
   }
+}
+
+// One chunk of one head, from a state of zeros, as three 32-bit products of 64 x 64 tiles
+// (a thread owns 4 x 4 sums): P = (Q K^T) * D with D[i][j] = decay^(i-j) for j <= i and 0
+// above; the chunk's read-outs O = P V; and what the chunk adds to the state,
+// sum_t decay^(rows-1-t) k_t v_t^T, left in the chunk's entry.
+#define RT_CT 64
+__global__ void __launch_bounds__(256) retention_chunk_kernel(const RetentionArgs a) {
+  extern __shared__ __align__(16) float rc_sm[];
+  float (*PsT)[RT_CT] = reinterpret_cast<float (*)[RT_CT]>(rc_sm);                     // [key row j][query row i]
+  float (*Vs)[RT_CT] = reinterpret_cast<float (*)[RT_CT]>(rc_sm + RT_CT * RT_CT);      // [row t][column]
+  float (*Kt)[RT_CT] = reinterpret_cast<float (*)[RT_CT]>(rc_sm + 2 * RT_CT * RT_CT);  // [row t][element], weighted
+  float (*Qs)[RT_CT] = reinterpret_cast<float (*)[RT_CT]>(rc_sm + 3 * RT_CT * RT_CT);  // [RT_TK][row]
+  float (*Ks)[RT_CT] = Qs + RT_TK;
+  float* dpow = rc_sm + 3 * RT_CT * RT_CT + 2 * RT_TK * RT_CT;                         // decay^0 .. decay^RT_CT
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  const int H = a.H, dk = a.dk, dv = a.dv;
+  const int h = blockIdx.x, seq = blockIdx.y, z = blockIdx.z;
+  const int first = a.cu_q[seq], n = a.cu_q[seq + 1] - first;
+  if (z * RT_CHUNK >= n) return;
+  const int rows = min(RT_CHUNK, n - z * RT_CHUNK), r0 = first + z * RT_CHUNK;
+  const int tid = threadIdx.x, ty = tid / 16, tx = tid % 16;
+  const int C = 2 * H * dk + 2 * H * dv;
+  const float decay = a.decay[h];
+  if (tid <= RT_CT) dpow[tid] = powf(decay, (float)tid);
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < dk; k0 += RT_TK) {
+    __syncthreads();
+    {
+      const int m = tid / 4, kk = (tid % 4) * 4;
+      const float* src = a.qk + ((size_t)(r0 + m) * 2 * H + h) * dk + k0 + kk;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const bool in = m < rows && k0 + kk + i < dk;
+        Qs[kk + i][m] = in ? src[i] : 0.f;
+        Ks[kk + i][m] = in ? src[(size_t)H * dk + i] : 0.f;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < RT_TK; ++kk) {
+      const float4 q4 = *reinterpret_cast<const float4*>(&Qs[kk][ty * 4]);
+      const float4 k4 = *reinterpret_cast<const float4*>(&Ks[kk][tx * 4]);
+      const float qv[4] = {q4.x, q4.y, q4.z, q4.w}, kv[4] = {k4.x, k4.y, k4.z, k4.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(qv[i], kv[j], acc[i][j]);
+    }
+  }
+  // P under the decay mask, stored with the key row first
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float pv[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int qi = ty * 4 + i, kj = tx * 4 + j;
+      pv[i] = kj <= qi ? acc[i][j] * dpow[qi - kj] : 0.f;
+    }
+    *reinterpret_cast<float4*>(&PsT[tx * 4 + j][ty * 4]) = make_float4(pv[0], pv[1], pv[2], pv[3]);
+  }
+  float* sp = a.chunk_state + (rt_entry(first, z, seq) * H + h) * (size_t)dk * dv;
+  for (int c0 = 0; c0 < dv; c0 += RT_CT) {
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < RT_CT * RT_CT / 256; ++i) {
+      const int idx = tid + i * 256, t = idx / RT_CT, c = idx % RT_CT;
+      Vs[t][c] = (t < rows && c0 + c < dv) ? a.proj[(size_t)(r0 + t) * C + 2 * H * dk + h * dv + c0 + c] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+#pragma unroll 8
+    for (int t = 0; t < RT_CT; ++t) {
+      const float4 p4 = *reinterpret_cast<const float4*>(&PsT[t][ty * 4]);
+      const float4 v4 = *reinterpret_cast<const float4*>(&Vs[t][tx * 4]);
+      const float pv[4] = {p4.x, p4.y, p4.z, p4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(pv[i], vv[j], acc[i][j]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int m = ty * 4 + i;
+      if (m >= rows) continue;
+      float* o = a.o + ((size_t)(r0 + m) * H + h) * dv + c0 + tx * 4;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (c0 + tx * 4 + j < dv) o[j] = acc[i][j];
+    }
+    for (int i0 = 0; i0 < dk; i0 += RT_CT) {
+      __syncthreads();
+#pragma unroll
+      for (int i = 0; i < RT_CT * RT_CT / 256; ++i) {
+        const int idx = tid + i * 256, t = idx / RT_CT, e = idx % RT_CT;
+        Kt[t][e] = (t < rows && i0 + e < dk)
+                       ? a.qk[((size_t)(r0 + t) * 2 * H + H + h) * dk + i0 + e] * dpow[rows - 1 - t] : 0.f;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+#pragma unroll 8
+      for (int t = 0; t < RT_CT; ++t) {
+        const float4 k4 = *reinterpret_cast<const float4*>(&Kt[t][ty * 4]);
+        const float4 v4 = *reinterpret_cast<const float4*>(&Vs[t][tx * 4]);
+        const float kv[4] = {k4.x, k4.y, k4.z, k4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(kv[i], vv[j], acc[i][j]);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int e = i0 + ty * 4 + i;
+        if (e >= dk) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (c0 + tx * 4 + j < dv) sp[(size_t)e * dv + c0 + tx * 4 + j] = acc[i][j];
+      }
+    }
+  }
+  pdl_launch_dependents_if_large();
 }
 
 // The states at the chunks' starts: a thread owns one element of a (sequence, head)'s
@@ -426,12 +545,20 @@ static int retention_step_launch(const RetentionArgs& a, cudaStream_t s) {
 }
 
 template <int KPL>
-static int retention_scan_launch(const RetentionArgs& a, cudaStream_t s, int chunks) {
-  const int groups = (a.dv + RT_COLS - 1) / RT_COLS;
-  if (chunks)
-    return gb_launch(retention_scan_kernel<KPL, true>, dim3(a.H, a.n_seqs, chunks * groups),
-                     dim3(RT_COLS * RT_LANES), 0, s, a);
-  return gb_launch(retention_scan_kernel<KPL, false>, dim3(a.H, a.n_seqs, groups), dim3(RT_COLS * RT_LANES), 0, s, a);
+static int retention_scan_launch(const RetentionArgs& a, cudaStream_t s) {
+  return gb_launch(retention_scan_kernel<KPL>, dim3(a.H, a.n_seqs, (a.dv + RT_COLS - 1) / RT_COLS),
+                   dim3(RT_COLS * RT_LANES), 0, s, a);
+}
+
+static int retention_chunk_launch(const RetentionArgs& a, cudaStream_t s, int chunks) {
+  const size_t smem = (size_t)(3 * RT_CT * RT_CT + 2 * RT_TK * RT_CT + RT_CT + 1) * sizeof(float);
+  static bool raised = false;    // more than the 48 KB a kernel gets without asking
+  if (!raised) {
+    cudaError_t ce = cudaFuncSetAttribute(retention_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (ce != cudaSuccess) return (int)ce;
+    raised = true;
+  }
+  return gb_launch(retention_chunk_kernel, dim3(a.H, a.n_seqs, chunks), dim3(256), smem, s, a);
 }
 
 template <typename T>
@@ -454,17 +581,16 @@ static int retention_forward(const RetentionArgs& a, cudaStream_t s) {
   if (e) return e;
   // a sequence of many rows goes chunk by chunk: every chunk alone from zeros and all at
   // once, then the states at the chunks' starts, then what those add to the read-outs
-  const int groups = (a.dv + RT_COLS - 1) / RT_COLS;
   int chunks = a.max_rows >= RT_CHUNK_MIN && a.chunk_state ? (a.max_rows + RT_CHUNK - 1) / RT_CHUNK : 0;
-  if ((long long)chunks * groups > 65535 || (long long)chunks * (RT_CHUNK / RT_TM) * ((a.dv + RT_TN - 1) / RT_TN) > 0x7fffffffLL)
-    chunks = 0;
+  if (chunks > 65535 || (long long)chunks * (RT_CHUNK / RT_TM) * ((a.dv + RT_TN - 1) / RT_TN) > 0x7fffffffLL) chunks = 0;
   const int kpl = (a.dk + RT_LANES - 1) / RT_LANES;
-  if (kpl <= 1) e = retention_scan_launch<1>(a, s, chunks);
-  else if (kpl <= 2) e = retention_scan_launch<2>(a, s, chunks);
-  else if (kpl <= 4) e = retention_scan_launch<4>(a, s, chunks);
-  else if (kpl <= 8) e = retention_scan_launch<8>(a, s, chunks);
-  else if (kpl <= 16) e = retention_scan_launch<16>(a, s, chunks);
-  else e = retention_scan_launch<32>(a, s, chunks);
+  if (chunks) e = retention_chunk_launch(a, s, chunks);
+  else if (kpl <= 1) e = retention_scan_launch<1>(a, s);
+  else if (kpl <= 2) e = retention_scan_launch<2>(a, s);
+  else if (kpl <= 4) e = retention_scan_launch<4>(a, s);
+  else if (kpl <= 8) e = retention_scan_launch<8>(a, s);
+  else if (kpl <= 16) e = retention_scan_launch<16>(a, s);
+  else e = retention_scan_launch<32>(a, s);
   if (e) return e;
   if (chunks) {
     e = gb_launch(retention_prefix_kernel, dim3((a.dk * a.dv + 255) / 256, a.H, a.n_seqs), dim3(256), 0, s, a);

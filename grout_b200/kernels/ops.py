@@ -1530,7 +1530,7 @@ class _RetentionArgs(ctypes.Structure):
                 ("k_scale", _F), ("norm_eps", _F), ("max_rows", _I)]
 
 
-RETENTION_CHUNK = 128        # rows of a chunk of the kernel's chunked scan
+RETENTION_CHUNK = 64         # rows of a chunk of the kernel's chunked form
 RETENTION_CHUNK_MIN = 256    # a sequence of this many rows in a step: the step goes chunk by chunk
 
 
@@ -1554,7 +1554,7 @@ def retention_forward(proj: torch.Tensor, state: torch.Tensor, decay: torch.Tens
     divided by its root mean square over dv (``norm_eps`` under the root), times silu(gate).
     ``max_rows``: the most rows any sequence of the step brings, when the caller knows it (a
     step of one row a sequence is one kernel; a step with a sequence of many rows runs all
-    chunks of 128 rows side by side and joins them through the states at their starts)."""
+    chunks of 64 rows side by side and joins them through the states at their starts)."""
     _need(proj, "projection", torch.float32, 2)
     _need(state, "state", torch.float32, 2)
     _need(decay, "decay", torch.float32, 1)
