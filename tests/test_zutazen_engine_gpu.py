@@ -321,7 +321,10 @@ def test_steps_that_mix_one_and_many_tokens(engines, oracle, name, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_captured_steps_against_steps_launched_one_by_one(engines, oracle, dtype):
-    """Bit-equal in 32-bit; both within the plain implementation's bar in bfloat16."""
+    """Both within the plain implementation's bar; in 32-bit equal to each other up to the
+    rounding of sums taken in another order (a captured prompt step knows only an upper
+    bound of the rows its sequences bring, so retention may go chunk by chunk there and row
+    by row in the launched step)."""
     reqs = [random_tokens(n, ZUT["Q"]["vocab"], 740 + i) for i, n in enumerate((90, 33, 140))]
     outs = {}
     for use in (True, False):
@@ -331,7 +334,7 @@ def test_captured_steps_against_steps_launched_one_by_one(engines, oracle, dtype
         assert_close(outs[True][i], oracle("Q", r), dtype, f"captured, request {i}")
         assert_close(outs[False][i], oracle("Q", r), dtype, f"launched, request {i}")
         if dtype == "float32":
-            assert torch.equal(outs[True][i], outs[False][i])
+            assert torch.allclose(outs[True][i], outs[False][i], atol=1e-5, rtol=1e-4)
 
 
 @pytest.mark.parametrize("name", sorted(ZUT))
