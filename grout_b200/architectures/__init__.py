@@ -1,2 +1,2 @@
 """Architectures known to the library; importing this package registers them."""
-from . import qwen3, sonalorn, suvazen, zutazen  # noqa: F401
+from . import mananex, qwen3, sonalorn, suvazen, zutazen  # noqa: F401

@@ -34,11 +34,14 @@ class KVSpec:
     """Keys and values of ``n_kv_heads`` heads of ``head_dim`` for every token
     (``window`` None) or for the last ``window`` tokens.  ``values_in_keys``: a
     token's value is read from its key row (a latent that serves as both), so the
-    store holds one tensor and hands it out as keys and as values."""
+    store holds one tensor and hands it out as keys and as values.  ``keep_first``:
+    with a window, a sequence's first ``keep_first`` tokens stay visible to every
+    later query, so the pages that hold them are never given back."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     values_in_keys: bool = False
+    keep_first: int = 0
 
     def make_store(self, n_layers: int, sizes: StoreSizes, dtype, device, allocate: bool = True):
         from .stores import KVStore
@@ -56,6 +59,19 @@ class StateSpec:
     def make_store(self, n_layers: int, sizes: StoreSizes, dtype, device, allocate: bool = True):
         from .stores import StateStore
         return StateStore(self, n_layers, sizes.max_slots, device, allocate)
+
+
+@dataclass(frozen=True)
+class SideBySideSpec:
+    """The needs of mixers that run side by side in one layer (keys and values for one,
+    a state for the other, ...): a store of each, opened, grown, trimmed and closed
+    together; the layer is handed the tuple of their views, in the order of ``specs``."""
+    specs: Tuple[object, ...]
+
+    def make_store(self, n_layers: int, sizes: StoreSizes, dtype, device, allocate: bool = True):
+        from .stores import SideBySideStore
+        return SideBySideStore(self, [s.make_store(n_layers, sizes, dtype, device, allocate)
+                                      for s in self.specs])
 
 
 class CacheFull(RuntimeError):

@@ -89,13 +89,15 @@ class KVStore:
 
     def trim(self, slot: int, length: int) -> None:
         """With a window: frees pages whose tokens no query at position >= length
-        can see any more (all their positions are <= length - window)."""
+        can see any more (all their positions are <= length - window, and none of
+        them is among the first ``keep_first``)."""
         w = self.spec.window
         if w is None:
             return
         pages = self.pages_of[slot]
         dead = max(0, length - w + 1) // PAGE_TOKENS   # pages [0, dead) are out of reach
-        for i in range(min(dead, len(pages))):
+        kept = pages_for(self.spec.keep_first)         # ... but for those with kept first tokens
+        for i in range(kept, min(dead, len(pages))):
             if pages[i] is not None:
                 self.pool.release(pages[i])
                 pages[i] = None
@@ -170,3 +172,41 @@ class StateStore:
 
     def check(self) -> None:
         pass
+
+
+class SideBySideStore:
+    """Several stores that serve one group of layers together (``SideBySideSpec``): every
+    call goes to each of them, and a layer's view is the tuple of their views."""
+
+    def __init__(self, spec, stores):
+        self.spec, self.stores = spec, list(stores)
+
+    def open(self, slot: int) -> None:
+        for st in self.stores:
+            st.open(slot)
+
+    def reserve(self, slot: int, n_tokens: int) -> None:
+        for st in self.stores:
+            st.reserve(slot, n_tokens)
+
+    def trim(self, slot: int, length: int) -> None:
+        for st in self.stores:
+            st.trim(slot, length)
+
+    def close(self, slot: int) -> None:
+        for st in self.stores:
+            st.close(slot)
+
+    def flush(self) -> None:
+        for st in self.stores:
+            st.flush()
+
+    def tokens_held(self) -> int:
+        return max((st.tokens_held() for st in self.stores), default=0)
+
+    def layer(self, index: int):
+        return tuple(st.layer(index) for st in self.stores)
+
+    def check(self) -> None:
+        for st in self.stores:
+            st.check()

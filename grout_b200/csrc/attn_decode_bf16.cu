@@ -39,6 +39,7 @@ struct DecodeArgs {
   float scale_log2;
   const float* sinks;      // [nq] one more logit of every head's denominator, or null
   ScoreCap cap;            // the score cap (off when cap_log2 == 0)
+  int keep_first;          // with a window: a sequence's first keep_first keys stay visible behind it
 };
 
 template <int DT>
@@ -60,17 +61,22 @@ __global__ void __launch_bounds__(DC_THREADS) attn_decode_kernel(const DecodeArg
   const int pos = kv_len - 1;
   const int key_lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
   const int tile_lo = key_lo / DC_BN;
-  const int n_tiles = kv_len > 0 ? pos / DC_BN - tile_lo + 1 : 0;
+  // With kept first keys the tiles in front of the window that hold some are visited too:
+  // the splits divide the list v = 0 .. n_tiles - 1, the kept tiles first, then the window's.
+  const int keep = a.window > 0 ? a.keep_first : 0;
+  const int n_kept = min((min(keep, key_lo) + DC_BN - 1) / DC_BN, tile_lo);
+  const int n_tiles = kv_len > 0 ? n_kept + pos / DC_BN - tile_lo + 1 : 0;
   const int per_split = (n_tiles + a.n_splits - 1) / a.n_splits;
-  const int t_begin = tile_lo + split * per_split;
-  const int t_end = min(tile_lo + n_tiles, t_begin + per_split);
+  const int t_begin = split * per_split;
+  const int t_end = min(n_tiles, t_begin + per_split);
   const bool empty = t_begin >= t_end;   // a padding row, or more splits than tiles
+  auto tile_of = [&](int v) { return v < n_kept ? v : tile_lo + v - n_kept; };
   // The producer kernel of this step wrote the queries and the key and value of
   // position kv_len - 1; everything else this block reads (slots, lengths, block
   // table, older keys) was there before the step.  So the tiles without the
   // newest key are requested before waiting for the producer, and its last
   // microseconds overlap the start of the key stream.
-  const int fresh_tile = pos / DC_BN;
+  const int fresh_tile = n_tiles - 1;     // (in the list's numbering)
 
   if (empty) {
     pdl_wait();
@@ -97,8 +103,9 @@ __global__ void __launch_bounds__(DC_THREADS) attn_decode_kernel(const DecodeArg
     // value buffer after the P.V product, so that with two buffers of each a tile and a half
     // are in flight on average, not one.  Every thread commits the groups in the order
     // K(0) V(0) K(1) V(1) ..., empty ones included, which is what the wait counts rely on.
-    auto load_half = [&](int tile, int stage, int which) {
-      if (tile < t_end) {
+    auto load_half = [&](int v, int stage, int which) {
+      if (v < t_end) {
+        const int tile = tile_of(v);
         const int pg = tpp_shift >= 0 ? tile >> tpp_shift : tile / tiles_per_page;
         const int in_page = tile - pg * tiles_per_page;
         const int page = table[pg];
@@ -142,6 +149,7 @@ __global__ void __launch_bounds__(DC_THREADS) attn_decode_kernel(const DecodeArg
     WarpAttn<DT> w;
     w.init();
     w.cap = a.cap;
+    w.keep = keep;
     int lo[2] = {key_lo, key_lo}, hi[2] = {pos, pos};
 #pragma unroll
     for (int s = 0; s < DC_STAGES; ++s) {   // what had to wait for the producer
@@ -160,7 +168,7 @@ __global__ void __launch_bounds__(DC_THREADS) attn_decode_kernel(const DecodeArg
     for (int tile = first; tile < t_end; tile += DC_WARPS, stage = stage + 1 == DC_STAGES ? 0 : stage + 1) {
       cp_async_wait<BEHIND>();
       __syncwarp();
-      const int key0 = tile * DC_BN;
+      const int key0 = tile_of(tile) * DC_BN;
       const bf16* kt = my + (stage * 2 + 0) * DC_BN * LD;
       const bf16* vt = my + (stage * 2 + 1) * DC_BN * LD;
       const int refill = tile + DC_STAGES * DC_WARPS;

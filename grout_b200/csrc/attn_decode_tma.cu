@@ -52,6 +52,7 @@ struct DecodeTmaArgs {
   unsigned long long* stamps;   // optional [blocks][12] %globaltimer stamps of a block's phases (tuning), or null
   const float* sinks;      // [nq] one more logit of every head's denominator, or null
   ScoreCap cap;            // the score cap (off when cap_log2 == 0)
+  int keep_first;          // with a window: a sequence's first keep_first keys stay visible behind it
 };
 
 #define DA_STAMP(slot)                                                                          \
@@ -97,16 +98,21 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
   const int pos = kv_len - 1;
   const int key_lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
   const int tile_lo = key_lo / DA_BN;
-  const int n_tiles = kv_len > 0 ? pos / DA_BN - tile_lo + 1 : 0;
+  // With kept first keys the tiles in front of the window that hold some are visited too:
+  // the splits divide the list v = 0 .. n_tiles - 1, the kept tiles first, then the window's.
+  const int keep = a.window > 0 ? a.keep_first : 0;
+  const int n_kept = min((min(keep, key_lo) + DA_BN - 1) / DA_BN, tile_lo);
+  const int n_tiles = kv_len > 0 ? n_kept + pos / DA_BN - tile_lo + 1 : 0;
   const int per_split = (n_tiles + a.n_splits - 1) / a.n_splits;
-  const int t_begin = tile_lo + split * per_split;
-  const int t_end = min(tile_lo + n_tiles, t_begin + per_split);
+  const int t_begin = split * per_split;
+  const int t_end = min(n_tiles, t_begin + per_split);
   const int my_tiles = max(0, t_end - t_begin);
+  auto tile_of = [&](int v) { return v < n_kept ? v : tile_lo + v - n_kept; };
   // The producer kernel of this step wrote the queries and the key and value of
   // position kv_len - 1; everything else this block reads (slots, lengths, block
   // table, older keys) was there before the step.  So the tiles without the
   // newest key are requested before waiting for that kernel.
-  const int fresh_tile = pos / DA_BN;
+  const int fresh_tile = n_tiles - 1;      // (in the list's numbering)
 
   if (tid == 0) DA_STAMP(0);
   if (tid == DA_CONSUMERS) {      // the producer lane: have the descriptors fetched while the block sets up
@@ -143,7 +149,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
           pdl_wait();
           waited = true;
         }
-        const int row0 = (table[tile] * a.nkv + kvh) * DA_BN;     // first row of the (page, kv head) tile
+        const int row0 = (table[tile_of(tile)] * a.nkv + kvh) * DA_BN;     // first row of the (page, kv head) tile
         unsigned char* st = stages + (size_t)s * STAGE_BYTES;
         mbar_expect_tx(&full_k[s], HALF_BYTES);
 #pragma unroll
@@ -167,6 +173,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
   WarpAttn<DT> w;
   w.init();
   w.cap = a.cap;
+  w.keep = keep;
   if (my_tiles > 0) {
     // the query tile: G rows, the rest zero
     const bf16* qsrc = a.q + ((size_t)seq * a.nq + h0) * D;
@@ -185,7 +192,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
     for (int it = 0; it < my_tiles && ok; ++it) {
       const int s = it % STAGES;
       const uint32_t parity = (it / STAGES) & 1;
-      const int key0 = (t_begin + it) * DA_BN + warp * 32;    // this warp's 32 keys of the tile
+      const int key_tile = tile_of(t_begin + it) * DA_BN;
+      const int key0 = key_tile + warp * 32;                  // this warp's 32 keys of the tile
       const bf16* kt = reinterpret_cast<const bf16*>(stages + (size_t)s * STAGE_BYTES);
       bf16* vt = reinterpret_cast<bf16*>(stages + (size_t)s * STAGE_BYTES + HALF_BYTES);
       if (!mbar_wait_warp(&full_k[s], parity, abort_flag)) {
@@ -193,7 +201,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
         break;
       }
       if (tid == 0 && it == 0) DA_STAMP(5);
-      const int valid = kv_len - (t_begin + it) * DA_BN;       // rows of the page that hold keys
+      const int valid = kv_len - key_tile;                     // rows of the page that hold keys
       bool wrote = false;
       auto between = [&] {
         ok = mbar_wait_warp(&full_v[s], parity, abort_flag);

@@ -9,7 +9,9 @@
 // the other sequences of the batch, or where its pages lie.
 // Scores are q.k * scale; key j is visible when j <= pos and, with a window W,
 // when j > pos - W (the reference masks with -1e30 instead of skipping,
-// src/kernels.rs:1190-1191, 1256; same result).  With a cap c > 0 a score s
+// src/kernels.rs:1190-1191, 1256; same result) or, with `keep_first` F, when j < F:
+// the first F tokens of a sequence stay visible behind the window, at their own
+// positions; they are visited first, then the window.  With a cap c > 0 a score s
 // becomes c * tanh(s / c); with sinks, exp(sinks[h]) is one more term of query
 // head h's denominator, without a value.
 #include "common.cuh"
@@ -25,7 +27,8 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, const T* __restrict
                                     const int* __restrict__ token_pos,
                                     const int* __restrict__ slots, T* __restrict__ out, int nq,
                                     int nkv, int D, int page, float scale, int window,
-                                    float softcap, const float* __restrict__ sinks) {
+                                    float softcap, const float* __restrict__ sinks,
+                                    int keep_first) {
   extern __shared__ float sm[];
   __shared__ float scratch[32];
   float* q_s = sm;       // [D]
@@ -50,9 +53,13 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, const T* __restrict
 #pragma unroll
   for (int i = 0; i < ATT_MAX_ACC; ++i) acc[i] = 0.f;
 
-  for (int c = lo; c <= pos; c += ATT_THREADS) {
+  // two runs of keys: the kept first tokens that lie in front of the window, then the window
+  const int kept = min(keep_first, lo);
+  for (int run = kept > 0 ? 0 : 1; run < 2; ++run) {
+  const int c_lo = run ? lo : 0, c_hi = run ? pos : kept - 1;
+  for (int c = c_lo; c <= c_hi; c += ATT_THREADS) {
     const int j = c + tid;
-    const bool valid = j <= pos;
+    const bool valid = j <= c_hi;
     float s = -INFINITY;
     if (valid) {
       const T* kr = k_pages + paged_row(table, j, kvh, nkv, page, D);
@@ -68,7 +75,7 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, const T* __restrict
     p_s[tid] = p;
     const float csum = block_sum(p, scratch);  // its barriers also publish p_s
     l = l * corr + csum;
-    const int n = min(ATT_THREADS, pos - c + 1);
+    const int n = min(ATT_THREADS, c_hi - c + 1);
 #pragma unroll
     for (int i = 0; i < ATT_MAX_ACC; ++i) acc[i] *= corr;
     for (int jj = 0; jj < n; ++jj) {
@@ -82,6 +89,7 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, const T* __restrict
     }
     m = m_new;
     __syncthreads();  // p_s is rewritten by the next chunk
+  }
   }
   if (sinks) {   // one more term of the denominator; it may be the largest
     const float sk = sinks[h];
@@ -103,7 +111,9 @@ template <typename T>
 static int launch(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                   int max_pages, const int* token_seq, const int* token_pos, const int* slots,
                   void* out, int n_tokens, int nq, int nkv, int D, int page, float scale,
-                  int window, float softcap, const float* sinks, cudaStream_t stream) {
+                  int window, float softcap, const float* sinks, int keep_first,
+                  cudaStream_t stream) {
+  if (keep_first < 0) return GB_ERR_BAD_ARG;
   if (n_tokens < 0 || nq <= 0 || nkv <= 0 || nq % nkv || D <= 0 || page <= 0 || max_pages <= 0)
     return GB_ERR_BAD_ARG;
   if (D > ATT_THREADS * ATT_MAX_ACC) return GB_ERR_UNSUPPORTED;
@@ -111,7 +121,8 @@ static int launch(const void* q, const void* k_pages, const void* v_pages, const
   const size_t smem = (size_t)(D + ATT_THREADS) * sizeof(float);
   attn_generic_kernel<T><<<dim3(n_tokens, nq), ATT_THREADS, smem, stream>>>(
       (const T*)q, (const T*)k_pages, (const T*)v_pages, block_table, max_pages, token_seq,
-      token_pos, slots, (T*)out, nq, nkv, D, page, scale, window, softcap, sinks);
+      token_pos, slots, (T*)out, nq, nkv, D, page, scale, window, softcap, sinks,
+      window > 0 ? keep_first : 0);
   return gb_status();
 }
 
@@ -119,15 +130,17 @@ GB_EXPORT int gb_attn_generic_f32(const void* q, const void* k_pages, const void
                                   const int* block_table, int max_pages, const int* token_seq,
                                   const int* token_pos, const int* slots, void* out, int n_tokens,
                                   int nq, int nkv, int D, int page, float scale, int window,
-                                  float softcap, const float* sinks, cudaStream_t s) {
+                                  float softcap, const float* sinks, int keep_first,
+                                  cudaStream_t s) {
   return launch<float>(q, k_pages, v_pages, block_table, max_pages, token_seq, token_pos, slots,
-                       out, n_tokens, nq, nkv, D, page, scale, window, softcap, sinks, s);
+                       out, n_tokens, nq, nkv, D, page, scale, window, softcap, sinks, keep_first, s);
 }
 GB_EXPORT int gb_attn_generic_bf16(const void* q, const void* k_pages, const void* v_pages,
                                    const int* block_table, int max_pages, const int* token_seq,
                                    const int* token_pos, const int* slots, void* out, int n_tokens,
                                    int nq, int nkv, int D, int page, float scale, int window,
-                                   float softcap, const float* sinks, cudaStream_t s) {
+                                   float softcap, const float* sinks, int keep_first,
+                                  cudaStream_t s) {
   return launch<bf16>(q, k_pages, v_pages, block_table, max_pages, token_seq, token_pos, slots,
-                      out, n_tokens, nq, nkv, D, page, scale, window, softcap, sinks, s);
+                      out, n_tokens, nq, nkv, D, page, scale, window, softcap, sinks, keep_first, s);
 }

@@ -116,9 +116,11 @@ struct WarpAttn {
   float o[2 * DT][4];               // 16 x D accumulator
   float m[2], l[2];                 // running max (already times c) and this lane's share of l
   ScoreCap cap;                     // the score cap, off after init()
+  int keep;                         // keys below it are seen whatever a row's lo (0 after init())
 
   __device__ __forceinline__ void init() {
     cap.cap_log2 = cap.cap_inv = 0.f;
+    keep = 0;
 #pragma unroll
     for (int i = 0; i < 2 * DT; ++i)
 #pragma unroll
@@ -137,7 +139,8 @@ struct WarpAttn {
 
   // One tile of NKEYS keys (a multiple of 16) held in shared memory as k_tile and
   // v_tile [NKEYS][LD].  Key index of tile row r is key0 + r.  Row `g` of this
-  // lane sees keys in [lo[0], hi[0]], row g + 8 keys in [lo[1], hi[1]].
+  // lane sees keys in [lo[0], hi[0]], row g + 8 keys in [lo[1], hi[1]]; both also see the
+  // keys below `keep` (the first tokens that a window keeps) up to their hi.
   template <int NKEYS, bool MASK>
   __device__ __forceinline__ void tile(const bf16* k_tile, const bf16* v_tile, int key0,
                                        const int (&lo)[2], const int (&hi)[2], float c) {
@@ -192,7 +195,7 @@ struct WarpAttn {
         float v = s[j][e] * c;
         if (MASK) {
           const int key = key0 + j * 8 + t * 2 + (e & 1);
-          if (key < lo[r] || key > hi[r]) v = -INFINITY;
+          if ((key < lo[r] && key >= keep) || key > hi[r]) v = -INFINITY;
         }
         s[j][e] = v;
         mx[r] = fmaxf(mx[r], v);

@@ -30,6 +30,7 @@ struct PrefillArgs {
   float scale_log2;        // scale * log2(e)
   const float* sinks;      // [nq] one more logit of every head's denominator, or null
   ScoreCap cap;            // the score cap (off when cap_log2 == 0)
+  int keep_first;          // with a window: a sequence's first keep_first keys stay visible behind it
 };
 
 template <int DT>
@@ -74,6 +75,12 @@ __global__ void __launch_bounds__(PF_THREADS) attn_prefill_kernel(const PrefillA
   const int key_hi = pos0 + rows - 1;
   const int key_lo = (a.window > 0 && pos0 - a.window + 1 > 0) ? pos0 - a.window + 1 : 0;
   const int tile_lo = key_lo / PF_BN, tile_hi = key_hi / PF_BN;
+  // The tiles in front of the window that hold kept first keys are visited first: the block
+  // walks v = 0 .. n_visit - 1, tile v of the kept ones, then the window's.
+  const int keep = a.window > 0 ? a.keep_first : 0;
+  const int n_kept = min((min(keep, key_lo) + PF_BN - 1) / PF_BN, tile_lo);
+  const int n_visit = n_kept + tile_hi - tile_lo + 1;
+  auto tile_of = [&](int v) { return v < n_kept ? v : tile_lo + v - n_kept; };
 
   auto load_tile = [&](int tile, int stage) {
     const int page = table[tile];
@@ -99,12 +106,13 @@ __global__ void __launch_bounds__(PF_THREADS) attn_prefill_kernel(const PrefillA
       cp_async16(q_s + r * LD + ch * 8, ok ? qsrc + (size_t)r * tok_stride + ch * 8 : qsrc, ok);
     }
   }
-  load_tile(tile_lo, 0);
+  load_tile(tile_of(0), 0);
   cp_async_commit();
 
   WarpAttn<DT> w;
   w.init();
   w.cap = a.cap;
+  w.keep = keep;
   // rows of this lane: warp * 16 + g and + 8
   int lo[2], hi[2];
 #pragma unroll
@@ -118,15 +126,16 @@ __global__ void __launch_bounds__(PF_THREADS) attn_prefill_kernel(const PrefillA
   const int warp_hi = pos0 + min(rows - 1, warp * 16 + 15);
   const int warp_lo = (a.window > 0) ? max(0, pos0 + warp * 16 - a.window + 1) : 0;
 
-  for (int tile = tile_lo; tile <= tile_hi; ++tile) {
-    const int stage = (tile - tile_lo) & 1;
-    if (tile + 1 <= tile_hi) load_tile(tile + 1, stage ^ 1);
+  for (int v = 0; v < n_visit; ++v) {
+    const int tile = tile_of(v);
+    const int stage = v & 1;
+    if (v + 1 < n_visit) load_tile(tile_of(v + 1), stage ^ 1);
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
-    if (tile == tile_lo) w.load_q(q_s + warp * 16 * LD);
+    if (v == 0) w.load_q(q_s + warp * 16 * LD);
     const int key0 = tile * PF_BN;
-    if (warp * 16 < rows && key0 <= warp_hi && key0 + PF_BN - 1 >= warp_lo) {
+    if (warp * 16 < rows && key0 <= warp_hi && (key0 + PF_BN - 1 >= warp_lo || key0 < keep)) {
       const bf16* kt = k_s + stage * PF_BN * LD;
       const bf16* vt = v_s + stage * PF_BN * LD;
       // tiles strictly below every row's own position and above every window edge need no mask

@@ -71,6 +71,7 @@ struct AttnTcArgs {
   float scale_log2;
   const float* sinks;      // [nq] one more logit of every head's denominator, or null
   ScoreCap cap;            // the score cap (off when cap_log2 == 0)
+  int keep_first;          // with a window: a sequence's first keep_first keys stay visible behind it
 };
 
 // V tile as the B operand of R = P V: N (head_dim) is the contiguous direction
@@ -245,9 +246,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   const int rows_a = min(rows, AT_BM), rows_b = rows - AT_BM;
   const int key_lo = (a.window > 0 && pos0 - a.window + 1 > 0) ? pos0 - a.window + 1 : 0;
   const int tile_lo = key_lo / AT_BN;
-  // tiles each query block needs (both start at tile_lo; A needs fewer at the end)
-  const int n_a = (pos0 + rows_a - 1) / AT_BN - tile_lo + 1;
-  const int n_b = has_b ? (pos0 + rows - 1) / AT_BN - tile_lo + 1 : 0;
+  // With kept first keys the tiles in front of the window that hold some come first in the
+  // list of tiles: entry j is tile j of the kept ones, then the window's tiles.
+  const int keep = a.window > 0 ? a.keep_first : 0;
+  const int n_kept = min((min(keep, key_lo) + AT_BN - 1) / AT_BN, tile_lo);
+  auto tile_of = [&](int j) { return j < n_kept ? j : tile_lo + j - n_kept; };
+  // tiles each query block needs (both start at the list's head; A needs fewer at the end)
+  const int n_a = n_kept + (pos0 + rows_a - 1) / AT_BN - tile_lo + 1;
+  const int n_b = has_b ? n_kept + (pos0 + rows - 1) / AT_BN - tile_lo + 1 : 0;
   const int n_tiles = has_b ? n_b : n_a;
 #ifdef AT_STAMPS
   long long* stamp_buf = (long long*)(a.error + 64);
@@ -302,7 +308,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           *abort_flag = 1;
           break;
         }
-        const int page = table[tile_lo + j];
+        const int page = table[tile_of(j)];
         const int row0 = (page * a.nkv + kvh) * AT_BN;
         uint8_t* st = kv_s + (size_t)s * Cfg::KV_BYTES;
         mbar_expect_tx(&kv_full[s], Cfg::KV_BYTES);
@@ -489,7 +495,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       const int b = j & 1;
       float s[AT_BN];
       float mx;
-      const int key0 = (tile_lo + j) * AT_BN;
+      const int key0 = tile_of(j) * AT_BN;
       const bool need_mask = j >= j_mask;
       AT_STAMP(stamp_buf, (g * 4 + (j - 8)) * 8 + 0)
       if (!wait_warp(&s_full[g], ((uint32_t)j) & 1)) { ok = false; break; }
@@ -514,9 +520,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         if (need_mask) {
           const int last = hi - key0, first = lo - key0;   // this row's keys of the tile
           if (a.window > 0) {
+            const int kept_below = keep - key0;            // keys of the tile that a window keeps
 #pragma unroll
             for (int c = 0; c < AT_BN; ++c)
-              if (c < first || c > last) s[c] = -INFINITY;
+              if ((c < first && c >= kept_below) || c > last) s[c] = -INFINITY;
           } else {
 #pragma unroll
             for (int c = 0; c < AT_BN; ++c)

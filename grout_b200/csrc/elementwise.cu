@@ -268,3 +268,44 @@ GB_EXPORT int gb_add_bias_f32(float* x, const float* bias, long long n_rows, int
   const size_t n = (size_t)n_rows * N;
   return gb_launch(add_bias_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, x, bias, n, N);
 }
+
+// A sigmoid gate per (row, head) on an attention's output, with a constant factor:
+// out[t, h * Dv + d] = x[t, h, d] * sigmoid(gate[t, h]) * mult for d < Dv.  x's heads are
+// Ds wide (Ds >= Dv: what lies beyond Dv is dropped); the gates' logits are 32-bit with a
+// row pitch of their own, and so has out, which may be part of a wider row.
+template <typename T>
+__global__ void head_gate_kernel(const T* __restrict__ x, const float* __restrict__ gate, long long gate_ld,
+                                 T* __restrict__ out, long long out_ld, int nq, int Ds, int Dv, float mult) {
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  const size_t t = blockIdx.y;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= nq * Dv) return;
+  const int h = i / Dv, d = i % Dv;
+  const float g = gate ? 1.0f / (1.0f + expf(-gate[t * gate_ld + h])) : 1.0f;
+  pdl_launch_dependents_if_large();
+  out[t * out_ld + i] = from_f32<T>(to_f32<T>(x[(t * nq + h) * Ds + d]) * g * mult);
+}
+template <typename T>
+static int head_gate(const void* x, const float* gate, long long gate_ld, void* out, long long out_ld,
+                     int n_rows, int nq, int Ds, int Dv, float mult, cudaStream_t s) {
+  if (n_rows < 0 || nq <= 0 || Dv <= 0 || Ds < Dv || !x || !out || out_ld < (long long)nq * Dv ||
+      (gate && gate_ld < nq))
+    return GB_ERR_BAD_ARG;
+  for (int r0 = 0; r0 < n_rows; r0 += 65535) {      // rows go to grid.y
+    const int n = n_rows - r0 < 65535 ? n_rows - r0 : 65535;
+    int e = gb_launch(head_gate_kernel<T>, dim3((nq * Dv + 255) / 256, n), dim3(256), 0, s,
+                      (const T*)x + (size_t)r0 * nq * Ds, gate ? gate + (size_t)r0 * gate_ld : gate, gate_ld,
+                      (T*)out + (size_t)r0 * out_ld, out_ld, nq, Ds, Dv, mult);
+    if (e) return e;
+  }
+  return 0;
+}
+GB_EXPORT int gb_head_gate_f32(const void* x, const float* gate, long long gate_ld, void* out, long long out_ld,
+                               int n_rows, int nq, int Ds, int Dv, float mult, cudaStream_t s) {
+  return head_gate<float>(x, gate, gate_ld, out, out_ld, n_rows, nq, Ds, Dv, mult, s);
+}
+GB_EXPORT int gb_head_gate_bf16(const void* x, const float* gate, long long gate_ld, void* out, long long out_ld,
+                                int n_rows, int nq, int Ds, int Dv, float mult, cudaStream_t s) {
+  return head_gate<bf16>(x, gate, gate_ld, out, out_ld, n_rows, nq, Ds, Dv, mult, s);
+}

@@ -1,0 +1,191 @@
+// Linear attention whose forget gate also decides what is written (HGRN2).  Per head,
+// with q, f [dk] and v [dv] of a token,
+//
+//   q = silu(zq),   f = low + (1 - low) * sigmoid(zf + bias)        (low: a learned floor per channel)
+//   S <- diag(f) S + (1 - f) v^T      (S [dk, dv], 32-bit, zero when the sequence starts)
+//   o  = S^T q
+//   y  = o / sqrt(mean(o^2) + eps) * w * out_scale                  (w [dv] shared by the heads)
+//
+// There is no key: 1 - f stands where a key would.  Everything here is 32-bit: the input
+// is the 32-bit sums of a projection (row pitch `ld`; zq, zf [H dk] and v [H dv] start at
+// the columns q_col, f_col, v_col), and only y is rounded to the activation type.  y's row
+// pitch is `y_ld`, so a head's read-out can be written into a wider row that another
+// kernel fills up (the input of an output projection that serves two mixers).
+//
+// Two kernels.  `scan` walks a sequence's rows in order: a block owns one (sequence,
+// head) and HG_COLS columns of S; a column's dk elements live in the registers of eight
+// lanes; the rows' q and f are computed from the sums HG_STAGE rows at a time into shared
+// memory, and the eight partial read-outs of a column meet by shuffles.  The state is read
+// once and written once per step, for sequences whose slot is not negative (padding rows
+// start from zeros and store nothing).  `finish` normalises a head's read-out.  The order
+// of a column's sums does not depend on how a sequence's rows are cut into steps, so a
+// prompt in one step, in portions or row by row leaves the same state bit for bit.
+#include "common.cuh"
+
+struct Hgrn2Args {
+  const float* proj;      // [T, ld]
+  long long ld;
+  int q_col, f_col, v_col;
+  const float* f_bias;    // [H dk]
+  const float* lower;     // [H dk]
+  const float* norm_w;    // [dv]
+  const int* cu_q;        // [n_seqs + 1]
+  const int* slots;       // [n_seqs]
+  float* state;           // [slots, state_stride], a sequence's H matrices [dk, dv]
+  long long state_stride;
+  float* o;               // [T, H, dv] scratch: the read-outs
+  void* y;                // [T, y_ld]: H dv columns are written
+  long long y_ld;
+  int n_tokens, n_seqs, H, dk, dv;
+  float norm_eps, out_scale;
+};
+
+#define HG_LANES 8      // lanes that share a column of the state
+#define HG_COLS 16      // columns a block owns
+#define HG_STAGE 16     // rows staged at a time
+
+__device__ __forceinline__ float hg_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+// Row r of a lane's share of a column is element hg_row(lane, r) of the head: runs of four
+// neighbours per lane where a lane has a multiple of four, else every eighth element.
+template <int KPL>
+__device__ __forceinline__ int hg_row(int lane, int r) {
+  return (KPL % 4 == 0) ? (r >> 2) * 32 + lane * 4 + (r & 3) : r * HG_LANES + lane;
+}
+
+template <int KPL>
+__global__ void __launch_bounds__(HG_COLS* HG_LANES) hgrn2_scan_kernel(const Hgrn2Args a) {
+  constexpr int DKP = KPL * HG_LANES;            // dk rounded up; the rest is q = 0, f = 1
+  __shared__ __align__(16) float qs[HG_STAGE][DKP];
+  __shared__ __align__(16) float fs[HG_STAGE][DKP];
+  __shared__ float vs[HG_STAGE][HG_COLS];
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  const int h = blockIdx.x, seq = blockIdx.y, c0 = blockIdx.z * HG_COLS;
+  const int dk = a.dk, dv = a.dv;
+  const int first = a.cu_q[seq], n = a.cu_q[seq + 1] - first;
+  if (n <= 0) return;
+  const int tid = threadIdx.x, lane = tid % HG_LANES, col = c0 + tid / HG_LANES;
+  const bool live = col < dv;
+  const int slot = a.slots[seq];
+  float* sp = slot >= 0 ? a.state + (size_t)slot * a.state_stride + (size_t)h * dk * dv : nullptr;
+  float S[KPL];
+#pragma unroll
+  for (int r = 0; r < KPL; ++r) {
+    const int i = hg_row<KPL>(lane, r);
+    S[r] = (sp && live && i < dk) ? sp[(size_t)i * dv + col] : 0.f;
+  }
+  for (int t0 = 0; t0 < n; t0 += HG_STAGE) {
+    const int nt = min(HG_STAGE, n - t0);
+    __syncthreads();
+    for (int i = tid; i < nt * DKP; i += blockDim.x) {
+      const int tt = i / DKP, e = i % DKP;
+      float q = 0.f, f = 1.f;
+      if (e < dk) {
+        const float* row = a.proj + (size_t)(first + t0 + tt) * a.ld;
+        const int c = h * dk + e;
+        const float zq = row[a.q_col + c], low = a.lower[c];
+        q = zq * hg_sigmoid(zq);
+        f = low + (1.0f - low) * hg_sigmoid(row[a.f_col + c] + a.f_bias[c]);
+      }
+      qs[tt][e] = q;
+      fs[tt][e] = f;
+    }
+    for (int i = tid; i < nt * HG_COLS; i += blockDim.x) {
+      const int tt = i / HG_COLS, c = c0 + i % HG_COLS;
+      vs[tt][i % HG_COLS] = c < dv ? a.proj[(size_t)(first + t0 + tt) * a.ld + a.v_col + h * dv + c] : 0.f;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float v = vs[tt][tid / HG_LANES];
+      float acc = 0.f;
+      if (KPL % 4 == 0) {
+#pragma unroll
+        for (int r = 0; r < KPL; r += 4) {
+          const float4 f4 = *reinterpret_cast<const float4*>(&fs[tt][hg_row<KPL>(lane, r)]);
+          const float4 q4 = *reinterpret_cast<const float4*>(&qs[tt][hg_row<KPL>(lane, r)]);
+          S[r] = fmaf(f4.x, S[r], (1.0f - f4.x) * v);
+          S[r + 1] = fmaf(f4.y, S[r + 1], (1.0f - f4.y) * v);
+          S[r + 2] = fmaf(f4.z, S[r + 2], (1.0f - f4.z) * v);
+          S[r + 3] = fmaf(f4.w, S[r + 3], (1.0f - f4.w) * v);
+          acc = fmaf(S[r], q4.x, acc);
+          acc = fmaf(S[r + 1], q4.y, acc);
+          acc = fmaf(S[r + 2], q4.z, acc);
+          acc = fmaf(S[r + 3], q4.w, acc);
+        }
+      } else {
+#pragma unroll
+        for (int r = 0; r < KPL; ++r) {
+          const int i = hg_row<KPL>(lane, r);
+          const float f = fs[tt][i];
+          S[r] = fmaf(f, S[r], (1.0f - f) * v);
+          acc = fmaf(S[r], qs[tt][i], acc);
+        }
+      }
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+      if (lane == 0 && live) a.o[((size_t)(first + t0 + tt) * a.H + h) * dv + col] = acc;
+    }
+  }
+  pdl_launch_dependents_if_large();
+  if (sp && live) {
+#pragma unroll
+    for (int r = 0; r < KPL; ++r) {
+      const int i = hg_row<KPL>(lane, r);
+      if (i < dk) sp[(size_t)i * dv + col] = S[r];
+    }
+  }
+}
+
+// One warp per (row, head): the read-out's root mean square, the weight, the factor.
+template <typename T>
+__global__ void __launch_bounds__(128) hgrn2_finish_kernel(const Hgrn2Args a) {
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long unit = (long long)blockIdx.x * 4 + warp;
+  if (unit >= (long long)a.n_tokens * a.H) return;
+  const int t = (int)(unit / a.H), h = (int)(unit % a.H), dv = a.dv;
+  const float* o = a.o + (size_t)unit * dv;
+  float ss = 0.f;
+  for (int d = lane; d < dv; d += 32) ss = fmaf(o[d], o[d], ss);
+  ss = warp_sum(ss);
+  const float inv = a.out_scale / sqrtf(ss / (float)dv + a.norm_eps);
+  T* y = (T*)a.y + (size_t)t * a.y_ld + (size_t)h * dv;
+  for (int d = lane; d < dv; d += 32) y[d] = from_f32<T>(o[d] * a.norm_w[d] * inv);
+  pdl_launch_dependents_if_large();
+}
+
+template <int KPL>
+static int launch_scan(const Hgrn2Args& a, cudaStream_t s) {
+  return gb_launch(hgrn2_scan_kernel<KPL>, dim3(a.H, a.n_seqs, (a.dv + HG_COLS - 1) / HG_COLS),
+                   dim3(HG_COLS * HG_LANES), 0, s, a);
+}
+
+template <typename T>
+static int launch(const Hgrn2Args& a, cudaStream_t s) {
+  if (a.n_tokens < 0 || a.n_seqs <= 0 || a.H <= 0 || a.dk <= 0 || a.dv <= 0 || !a.proj || !a.state ||
+      !a.o || !a.y || !a.f_bias || !a.lower || !a.norm_w || !a.cu_q || !a.slots)
+    return GB_ERR_BAD_ARG;
+  if (a.dk > 256 || a.n_seqs > 65535) return GB_ERR_UNSUPPORTED;
+  if (a.n_tokens == 0) return 0;
+  const int kpl = (a.dk + HG_LANES - 1) / HG_LANES;
+  int e;
+  if (kpl <= 1) e = launch_scan<1>(a, s);
+  else if (kpl <= 2) e = launch_scan<2>(a, s);
+  else if (kpl <= 3) e = launch_scan<3>(a, s);
+  else if (kpl <= 4) e = launch_scan<4>(a, s);
+  else if (kpl <= 6) e = launch_scan<6>(a, s);
+  else if (kpl <= 8) e = launch_scan<8>(a, s);
+  else if (kpl <= 12) e = launch_scan<12>(a, s);
+  else if (kpl <= 16) e = launch_scan<16>(a, s);
+  else if (kpl <= 24) e = launch_scan<24>(a, s);
+  else e = launch_scan<32>(a, s);
+  if (e) return e;
+  const long long units = (long long)a.n_tokens * a.H;
+  return gb_launch(hgrn2_finish_kernel<T>, dim3((unsigned)((units + 3) / 4)), dim3(128), 0, s, a);
+}
+
+GB_EXPORT int gb_hgrn2_f32(const Hgrn2Args* a, cudaStream_t s) { return launch<float>(*a, s); }
+GB_EXPORT int gb_hgrn2_bf16(const Hgrn2Args* a, cudaStream_t s) { return launch<bf16>(*a, s); }

@@ -11,7 +11,8 @@
 //   out = sum over the chosen of s * y
 //
 // Each of these terms is an argument.  `score_fn` 1 takes s = sigmoid(z), every output
-// by itself, instead of the softmax; `correction` may be null (no correction); a limit
+// by itself, instead of the softmax; `score_fn` 2 lets the logits z choose and takes the
+// softmax over the chosen logits alone as the weights; `router_bias` is added to z; `correction` may be null (no correction); a limit
 // of +inf clamps nothing; `up_offset` is the 1 in (u + 1) and may be 0; with
 // `weigh_input` the weight multiplies the expert's input instead of its result,
 // y = expert(s x): gate and up have no bias, so their 32-bit sums are multiplied by s
@@ -45,9 +46,10 @@ struct MoeArgs {
   float* out;               // [top, T, W]
   int T, W, F, E, n_identity, top, n_groups, keep_groups;
   float limit, slope;
-  int score_fn;              // 0: softmax over the outputs, 1: sigmoid of each
+  int score_fn;              // 0: softmax over the outputs, 1: sigmoid of each, 2: softmax over the chosen
   int weigh_input;           // the weight multiplies the expert's input, not its result
   float up_offset;           // y = act(g) (u + up_offset)
+  const float* router_bias;  // [E + n_identity] added to z, or null
 };
 
 #define MOE_MAX_OUTPUTS 1024
@@ -92,7 +94,7 @@ __global__ void __launch_bounds__(MOE_ROUTE_THREADS) moe_route_kernel(const MoeA
     if (tid < MOE_ROUTE_CHUNK && e0 + tid < n_all) {
       float v = 0.f;
       for (int w = 0; w < nwarps; ++w) v += part[w][tid];
-      z[e0 + tid] = v;
+      z[e0 + tid] = v + (a.router_bias ? a.router_bias[e0 + tid] : 0.f);
     }
     __syncthreads();
   }
@@ -100,6 +102,8 @@ __global__ void __launch_bounds__(MOE_ROUTE_THREADS) moe_route_kernel(const MoeA
     float mx = -INFINITY, sum = 0.f;
     if (a.score_fn == 1) {
       for (int e = 0; e < n_all; ++e) z[e] = 1.0f / (1.0f + expf(-z[e]));
+    } else if (a.score_fn == 2) {
+      // the logits themselves choose; the chosen ones' weights are worked out below
     } else {
       for (int e = 0; e < n_all; ++e) mx = fmaxf(mx, z[e]);
       for (int e = 0; e < n_all; ++e) { z[e] = expf(z[e] - mx); sum += z[e]; }
@@ -134,6 +138,13 @@ __global__ void __launch_bounds__(MOE_ROUTE_THREADS) moe_route_kernel(const MoeA
       c[best] = NAN;                    // taken
       a.ids[(size_t)t * a.top + j] = best;
       a.wts[(size_t)t * a.top + j] = z[best];
+    }
+    if (a.score_fn == 2) {              // softmax over the chosen logits alone; the first is the largest
+      float* w = a.wts + (size_t)t * a.top;
+      const float top_z = w[0];
+      float sum = 0.f;
+      for (int j = 0; j < a.top; ++j) { w[j] = expf(w[j] - top_z); sum += w[j]; }
+      for (int j = 0; j < a.top; ++j) w[j] = w[j] / sum;
     }
   }
   __syncthreads();
@@ -491,7 +502,7 @@ static int moe_check(const MoeArgs& a) {
   const int n_all = a.E + a.n_identity;
   if (n_all % a.n_groups || a.top > n_all) return GB_ERR_BAD_ARG;
   if (n_all > MOE_MAX_OUTPUTS) return GB_ERR_UNSUPPORTED;
-  if (a.score_fn < 0 || a.score_fn > 1) return GB_ERR_BAD_ARG;
+  if (a.score_fn < 0 || a.score_fn > 2) return GB_ERR_BAD_ARG;
   if (!a.x || !a.router_w || !a.w_gate || !a.w_up || !a.w_down || !a.ids || !a.wts ||
       !a.rank || !a.counts || !a.offsets || !a.perm || !a.act || !a.out)
     return GB_ERR_BAD_ARG;

@@ -1,6 +1,7 @@
 // Per (token, head) preparation of the fused q|k|v projection output:
 // RMSNorm over head_dim with a weight vector shared by all heads (optional),
-// then the half-split rotation of the first `rot_dim` elements (optional), then
+// then the rotation of the first `rot_dim` elements (optional; half-split pairs, or
+// with `interleaved` neighbours as pairs), then
 // q goes to q_out and k, v go into the paged cache at the token's position
 // (and/or to a dense kv_out).  The normalised value is not rounded before the
 // rotation: one rounding at the store, as in the reference's
@@ -31,6 +32,7 @@ struct QkPrepareArgs {
   int Ds;                   // width of a row of q_out, kv_out and the pages (0: D); the rest is zeros
   float q_temp_coef;        // with q_temp_every > 0 a query at position p is multiplied, after its
   int q_temp_every;         //   norm, by 1 + coef * ln(floor((p + 1) / every) + 1)
+  int interleaved;          // the rotation pairs element 2j with 2j + 1 instead of j with j + rot_dim / 2
 };
 
 __device__ __forceinline__ float query_temperature(const QkPrepareArgs& a, int pos) {
@@ -113,9 +115,10 @@ __global__ void qk_prepare_kernel(const QkPrepareArgs a) {
       const float angle = (float)pos * a.inv_freq[j];
       float s, c;
       sincosf(angle, &s, &c);
-      const float lo = x[j], hi = x[j + half];
-      x[j] = lo * c - hi * s;
-      x[j + half] = hi * c + lo * s;
+      const int i0 = a.interleaved ? 2 * j : j, i1 = a.interleaved ? 2 * j + 1 : j + half;
+      const float lo = x[i0], hi = x[i1];
+      x[i0] = lo * c - hi * s;
+      x[i1] = hi * c + lo * s;
     }
     __syncwarp();
   }
@@ -463,11 +466,19 @@ __global__ void __launch_bounds__(128) qk_prepare_chunk_kernel(const QkPrepareAr
   }
   __syncthreads();
   // this lane's part in the rotation: none, the first of a pair, or the second
-  const int role = (!a.inv_freq || j0 >= a.rot_dim) ? 0 : (j0 < half ? 1 : 2);
+  // (with neighbours as pairs both elements of a pair are this lane's own: no partner lane)
+  const int role = (!a.inv_freq || j0 >= a.rot_dim) ? 0 : (a.interleaved ? 3 : (j0 < half ? 1 : 2));
   const int partner = role == 1 ? lane + (half >> 3) : (role == 2 ? lane - (half >> 3) : lane);
   float sn[8], cs[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) {
+    if (role == 3) {
+      const bool turns = j0 + e < a.rot_dim;
+      sn[e] = turns ? sc_s[(j0 + e) >> 1] : 0.f;
+      cs[e] = turns ? sc_s[half + ((j0 + e) >> 1)] : 1.f;
+      if (!(e & 1)) sn[e] = -sn[e];
+      continue;
+    }
     sn[e] = role ? sc_s[(j0 + e) % half] : 0.f;
     cs[e] = role ? sc_s[half + (j0 + e) % half] : 1.f;
     if (role == 1) sn[e] = -sn[e];               // x cos - partner sin; the second: x cos + partner sin
@@ -541,7 +552,7 @@ __global__ void __launch_bounds__(128) qk_prepare_chunk_kernel(const QkPrepareAr
       float y[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
-        const float other = __shfl_sync(0xffffffffu, x[e], partner);
+        const float other = a.interleaved ? x[e ^ 1] : __shfl_sync(0xffffffffu, x[e], partner);
         y[e] = x[e] * cs[e] + other * sn[e];
       }
       if (kind != 2) {
@@ -569,7 +580,7 @@ static bool chunk_ok(const QkPrepareArgs& a) {
   auto al = [](const void* p) { return (((uintptr_t)p) & 15) == 0; };
   const int lph = a.D / 8;
   return a.D % 8 == 0 && lph <= 32 && (lph & (lph - 1)) == 0 &&
-         (!a.inv_freq || ((a.rot_dim / 2) % 8 == 0 && a.rot_dim <= 1024)) && al(a.qkv) && al(a.q_out) &&
+         (!a.inv_freq || ((a.interleaved || (a.rot_dim / 2) % 8 == 0) && a.rot_dim <= 1024)) && al(a.qkv) && al(a.q_out) &&
          al(a.kv_out) && al(a.k_pages) && al(a.v_pages) && al(a.qkv_parts) && (a.part_stride & 3) == 0;
 }
 
@@ -622,7 +633,7 @@ static int launch_fast(const QkPrepareArgs& a, cudaStream_t stream) {
 }
 
 static bool fast_ok(const QkPrepareArgs& a) {
-  return (a.D == 64 || a.D == 128 || a.D == 256) && (!a.inv_freq || a.rot_dim == a.D) &&
+  return (a.D == 64 || a.D == 128 || a.D == 256) && (!a.inv_freq || (a.rot_dim == a.D && !a.interleaved)) &&
          !a.v_from_k;
 }
 

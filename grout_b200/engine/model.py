@@ -11,7 +11,7 @@ import torch
 
 from ..cache import CacheLayout, SequenceCache
 from ..parts.base import BuildContext, ParamSpec, Part, build_part
-from ..parts.norm import with_offset
+from ..parts.norm import Averaged, with_offset
 from ..parts.plan import ModelPlan
 from .batch import StepContext
 
@@ -32,6 +32,7 @@ class Model:
         self.head = build_part("head", plan.head, ctx)
         self._layout: Optional[CacheLayout] = None
         self.stream_vectors: Dict[str, torch.Tensor] = {}    # 32-bit [rows, hidden] each
+        self.averages: Dict[int, torch.Tensor] = {}          # schedule index -> 32-bit weights of its depth average
 
     # -- tensors -----------------------------------------------------------
     def _named_parts(self) -> List[Tuple[str, Part]]:
@@ -58,6 +59,11 @@ class Model:
             if name in exp:
                 raise ValueError(f"two parts read tensor '{name}'")
             exp[name] = ParamSpec(tuple(shape), "offset")
+        for k, e in enumerate(self.plan.schedule):
+            if e.average is not None:
+                if e.average in exp:
+                    raise ValueError(f"two parts read tensor '{e.average}'")
+                exp[e.average] = ParamSpec((k + 2,), "average")
         for name, shape in self.plan.unread_tensors:
             exp.setdefault(name, ParamSpec(tuple(shape), "vector", optional=True))
         return exp
@@ -72,6 +78,8 @@ class Model:
             self.head.tie(self.embedding.weight)
         for name, _shape in self.plan.stream_vectors:     # added in 32-bit, as the stream is
             self.stream_vectors[name] = get(name).float().contiguous()
+        self.averages = {k: get(e.average).float().contiguous()
+                         for k, e in enumerate(self.plan.schedule) if e.average is not None}
 
     # -- cache -------------------------------------------------------------
     def cache_layout(self) -> CacheLayout:
@@ -100,7 +108,19 @@ class Model:
         """Runs the step's tokens through every scheduled layer; returns 32-bit
         logits [n_want, vocab] at ``step.want_rows`` (None when nothing is wanted)."""
         layout = self.cache_layout()
-        pending = self.embedding.forward(step.tokens, step)
+        history = None
+        if self.averages:
+            # a depth-averaged stream: the embedding's output and every entry's result are
+            # kept (32-bit) for the weighted sums behind the entries; the stream itself
+            # starts as a copy of the first, since it is updated in place
+            if not self.embedding.starts_stream:
+                raise ValueError("a depth-averaged stream starts from a 32-bit embedding")
+            history = torch.empty((len(self.plan.schedule) + 1, step.n_tokens, self.embedding.hidden),
+                                  dtype=torch.float32, device=step.tokens.device)
+            self.embedding.forward(step.tokens, step, out=history[0])
+            pending = self.embedding.forward(step.tokens, step)
+        else:
+            pending = self.embedding.forward(step.tokens, step)
         res = None
         if self.embedding.starts_stream:      # the embedding is the 32-bit stream already
             res, pending = pending, None
@@ -110,6 +130,8 @@ class Model:
             if e.add is not None:
                 pending = with_offset(pending, self.stream_vectors[e.add[0]][e.add[1]])
             res, pending = self.blocks[e.layer].forward(res, pending, step, view)
+            if history is not None:
+                pending = Averaged(pending, history, i + 1, self.averages[i])
         if step.n_want == 0:
             return None
         _res, h = self.final_norm.add_norm(res, pending, rows=step.want_rows)

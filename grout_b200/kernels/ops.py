@@ -246,13 +246,20 @@ def embed(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
     return out
 
 
-@_profiled("embed_scaled", lambda out, table, ids, scale: (_nbytes(ids, out) + out.numel() * table.element_size(), 0))
-def embed_scaled(table: torch.Tensor, ids: torch.Tensor, scale: float) -> torch.Tensor:
-    """scale * table[ids[t]] as 32-bit rows [T, H] (the product is 32-bit whatever the table's type)."""
+@_profiled("embed_scaled", lambda out, table, ids, scale, **k: (_nbytes(ids, out) + out.numel() * table.element_size(), 0))
+def embed_scaled(table: torch.Tensor, ids: torch.Tensor, scale: float,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """scale * table[ids[t]] as 32-bit rows [T, H] (the product is 32-bit whatever the table's
+    type), written into ``out`` when given."""
     _need(table, "embedding table", ndim=2)
     _need(ids, "token ids", torch.int32, 1)
     V, H = table.shape
-    out = torch.empty((ids.shape[0], H), dtype=torch.float32, device=table.device)
+    if out is None:
+        out = torch.empty((ids.shape[0], H), dtype=torch.float32, device=table.device)
+    else:
+        _need(out, "embedding output", torch.float32, 2)
+        if tuple(out.shape) != (ids.shape[0], H):
+            raise KernelError(f"the output is {tuple(out.shape)}, expected {(ids.shape[0], H)}")
     _check(_fn("embed", f"gb_embed_scaled_{_suffix(table.dtype)}", "ppfpiiip")(
         table.data_ptr(), ids.data_ptr(), float(scale), out.data_ptr(), ids.shape[0], H, V, _stream()),
         "embed_scaled")
@@ -473,7 +480,7 @@ class _QkPrepareArgs(ctypes.Structure):
                 ("n_tokens", _I), ("nq", _I), ("nkv", _I), ("D", _I), ("rot_dim", _I),
                 ("max_pages", _I), ("page", _I), ("qkv_parts", _P), ("n_parts", _I),
                 ("part_stride", _L), ("v_from_k", _I), ("Dv", _I), ("Ds", _I),
-                ("q_temp_coef", _F), ("q_temp_every", _I)]
+                ("q_temp_coef", _F), ("q_temp_every", _I), ("interleaved", _I)]
 
 
 @_profiled("qk_prepare", lambda out, qkv, nq, nkv, D, **k: _cost_qk_prepare(out, qkv, nq, nkv, D))
@@ -481,7 +488,8 @@ def qk_prepare(qkv: torch.Tensor, nq: int, nkv: int, D: int, *, q_w=None, k_w=No
                eps: float = 0.0, inv_freq=None, rot_dim: int = 0, token_seq, token_pos, slots,
                block_table=None, k_pages=None, v_pages=None, page: int = 0,
                want_kv_out: bool = False, values_are_keys: bool = False,
-               v_dim: Optional[int] = None, q_temp: Optional[Tuple[float, int]] = None):
+               v_dim: Optional[int] = None, q_temp: Optional[Tuple[float, int]] = None,
+               interleaved: bool = False):
     """Returns (q [T, nq, Ds], kv_out or None); writes k, v into the pages when given.
     ``qkv`` may be a stack of 32-bit partial sums [S, T, width] of the projection
     (bf16 engines only): they are added in order.  ``values_are_keys``: the
@@ -490,7 +498,8 @@ def qk_prepare(qkv: torch.Tensor, nq: int, nkv: int, D: int, *, q_w=None, k_w=No
     rows that are written (q, kv_out, pages) are then Ds wide, Ds being the pages'
     row width (at least D and ``v_dim``) or, without pages, the larger of the two,
     and end in zeros.  ``q_temp`` = (coef, every): a query at position p is
-    multiplied, after its norm, by 1 + coef * ln(floor((p + 1) / every) + 1)."""
+    multiplied, after its norm, by 1 + coef * ln(floor((p + 1) / every) + 1).
+    ``interleaved``: the rotation pairs element 2j with 2j + 1 (else j with j + rot_dim / 2)."""
     parts = None
     if qkv.dim() == 3:
         _need(qkv, "qkv partial sums", torch.float32, 3)
@@ -538,6 +547,7 @@ def qk_prepare(qkv: torch.Tensor, nq: int, nkv: int, D: int, *, q_w=None, k_w=No
     a.q_out, a.kv_out = q.data_ptr(), _ptr(kv_out)
     a.eps, a.n_tokens, a.nq, a.nkv, a.D, a.rot_dim = float(eps), T, nq, nkv, D, int(rot_dim)
     a.v_from_k = int(values_are_keys)
+    a.interleaved = int(bool(interleaved) and inv_freq is not None)
     a.Dv, a.Ds = Dv, Ds
     if q_temp:
         a.q_temp_coef, a.q_temp_every = float(q_temp[0]), int(q_temp[1])
@@ -599,16 +609,16 @@ def _check_sinks(sinks, nq: int) -> None:
 @_profiled("attn_generic", lambda out, q, *a, **k: (_nbytes(q, out), 0))
 def attn_generic(q, k_pages, v_pages, block_table, *, token_seq, token_pos, slots, page: int,
                  scale: float, window: Optional[int] = None, softcap: Optional[float] = None,
-                 sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 sinks: Optional[torch.Tensor] = None, keep_first: int = 0) -> torch.Tensor:
     T, nq, nkv, D = _attn_common(q, k_pages, v_pages, block_table, token_seq, token_pos, slots, page)
     _check_sinks(sinks, nq)
     out = torch.empty_like(q)
     sfx = _suffix(q.dtype)
-    _check(_fn("attn_generic", f"gb_attn_generic_{sfx}", "ppppippppiiiiififpp")(
+    _check(_fn("attn_generic", f"gb_attn_generic_{sfx}", "ppppippppiiiiififpip")(
         q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], token_seq.data_ptr(), token_pos.data_ptr(), slots.data_ptr(),
         out.data_ptr(), T, nq, nkv, D, page, float(scale), int(window or 0), float(softcap or 0.0),
-        _ptr(sinks), _stream()), "attn_generic")
+        _ptr(sinks), int(keep_first or 0), _stream()), "attn_generic")
     return out
 
 
@@ -1060,7 +1070,8 @@ class _PrefillArgs(ctypes.Structure):
     _fields_ = [("q", _P), ("k_pages", _P), ("v_pages", _P), ("block_table", _P), ("cu_q", _P),
                 ("slots", _P), ("kv_len", _P), ("out", _P), ("n_seqs", _I), ("nq", _I),
                 ("nkv", _I), ("max_pages", _I), ("window", _I), ("n_qblocks", _I),
-                ("scale_log2", _F), ("sinks", _P), ("cap_log2", _F), ("cap_inv", _F)]
+                ("scale_log2", _F), ("sinks", _P), ("cap_log2", _F), ("cap_inv", _F),
+                ("keep_first", _I)]
 
 
 class _DecodeArgs(ctypes.Structure):
@@ -1068,7 +1079,7 @@ class _DecodeArgs(ctypes.Structure):
                 ("kv_len", _P), ("out", _P), ("part_o", _P), ("part_ml", _P), ("n_seqs", _I),
                 ("nq", _I), ("nkv", _I), ("max_pages", _I), ("page", _I), ("window", _I),
                 ("n_splits", _I), ("scale_log2", _F), ("sinks", _P), ("cap_log2", _F),
-                ("cap_inv", _F)]
+                ("cap_inv", _F), ("keep_first", _I)]
 
 
 def _set_cap_and_sinks(a, scale: float, softcap: Optional[float], sinks, nq: int) -> None:
@@ -1128,9 +1139,9 @@ def _q_blocks(q_lens, n_qblocks, rows: int, T: int, n_seqs: int) -> int:
 def attn_prefill_bf16(q, k_pages, v_pages, block_table, *, cu_q, slots, kv_len, q_lens=(),
                       page: int, scale: float, window: Optional[int] = None,
                       n_qblocks: Optional[int] = None, softcap: Optional[float] = None,
-                      sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      sinks: Optional[torch.Tensor] = None, keep_first: int = 0) -> torch.Tensor:
     """Causal attention of whole prompts (or their continuation) on the tensor
-    cores.  The grid is sized from ``q_lens``, the host's copy of the sequences'
+    cores.  ``keep_first``: with a window, a sequence's first keys that stay visible behind it.  The grid is sized from ``q_lens``, the host's copy of the sequences'
     row counts, or, without them, from ``n_qblocks`` (an upper bound of the
     64-row blocks; by default the most the rows and sequences can make)."""
     T, nq, D = q.shape
@@ -1153,6 +1164,7 @@ def attn_prefill_bf16(q, k_pages, v_pages, block_table, *, cu_q, slots, kv_len, 
     a.window = int(window or 0)
     a.n_qblocks = _q_blocks(q_lens, n_qblocks, PREFILL_ROWS, T, n_seqs)
     a.scale_log2 = float(scale) * _LOG2E
+    a.keep_first = int(keep_first or 0)
     _set_cap_and_sinks(a, scale, softcap, sinks, nq)
     _check(_fn("attn_prefill_bf16", "gb_attn_prefill_bf16", "piip")(
         ctypes.addressof(a), D, page, _stream()), "attn_prefill_bf16")
@@ -1163,7 +1175,7 @@ class _AttnTcArgs(ctypes.Structure):
     _fields_ = [("block_table", _P), ("cu_q", _P), ("slots", _P), ("kv_len", _P), ("out", _P),
                 ("error", _P), ("n_seqs", _I), ("nq", _I), ("nkv", _I), ("max_pages", _I),
                 ("window", _I), ("n_qblocks", _I), ("scale_log2", _F), ("sinks", _P),
-                ("cap_log2", _F), ("cap_inv", _F)]
+                ("cap_log2", _F), ("cap_inv", _F), ("keep_first", _I)]
 
 
 PREFILL_TC_ROWS = 0        # query rows per block of the tcgen05 prefill kernel: 128, 256 or 0 = by size
@@ -1188,7 +1200,7 @@ def attn_prefill_tc(q, k_pages, v_pages, block_table, *, cu_q, slots, kv_len, q_
                     page: int, scale: float, window: Optional[int] = None,
                     rows_per_block: int = 0, n_qblocks: Optional[int] = None,
                     softcap: Optional[float] = None,
-                    sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    sinks: Optional[torch.Tensor] = None, keep_first: int = 0) -> torch.Tensor:
     """Causal attention of whole prompts (or their continuation) with both
     products on the tcgen05 tensor cores.  Pages must hold finite values in the
     rows beyond a sequence's length (the cache zero-fills its pages).  The grid is
@@ -1217,6 +1229,7 @@ def attn_prefill_tc(q, k_pages, v_pages, block_table, *, cu_q, slots, kv_len, q_
         prefill_tc_rows(_q_blocks(q_lens, None, 256, T, n_seqs), nq, q.device)
     a.n_qblocks = _q_blocks(q_lens, n_qblocks, rows, T, n_seqs)
     a.scale_log2 = float(scale) * _LOG2E
+    a.keep_first = int(keep_first or 0)
     _set_cap_and_sinks(a, scale, softcap, sinks, nq)
     _check(_fn("attn_prefill_tc", "gb_attn_prefill_tc", "ppppiliiip")(
         q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), ctypes.addressof(a), T,
@@ -1244,18 +1257,22 @@ def decode_splits(n_seqs: int, nkv: int, max_kv_len: int, device) -> int:
     return min(s for s, c in cost.items() if c <= 1.03 * best)
 
 
-def _keys_visited(max_kv_len: int, window: Optional[int], page: int) -> int:
+def _keys_visited(max_kv_len: int, window: Optional[int], page: int, keep_first: int = 0) -> int:
     """The most keys a decode row reads: its sequence's, or with a window the
-    window's, rounded out to the tiles that hold them."""
-    return min(max_kv_len, window + page - 1) if window else max_kv_len
+    window's and the kept first ones, rounded out to the tiles that hold them."""
+    if not window:
+        return max_kv_len
+    kept = (int(keep_first or 0) + page - 1) // page * page
+    return min(max_kv_len, window + page - 1 + kept)
 
 
 @_profiled("attn_decode_bf16", _cost_attention)
 def attn_decode_bf16(q, k_pages, v_pages, block_table, *, slots, kv_len, page: int, scale: float,
                      max_kv_len: int, window: Optional[int] = None,
                      n_splits: Optional[int] = None, softcap: Optional[float] = None,
-                     sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Attention of one new token per sequence over its cached keys (split-K)."""
+                     sinks: Optional[torch.Tensor] = None, keep_first: int = 0) -> torch.Tensor:
+    """Attention of one new token per sequence over its cached keys (split-K).
+    ``keep_first``: with a window, a sequence's first keys that stay visible behind it."""
     _need(q, "q", torch.bfloat16, 3)
     B, nq, D = q.shape
     _need(k_pages, "k pages", torch.bfloat16, 4)
@@ -1268,8 +1285,8 @@ def attn_decode_bf16(q, k_pages, v_pages, block_table, *, slots, kv_len, page: i
     if slots.shape[0] != B or kv_len.shape[0] != B:
         raise KernelError("one slot and one length per query row are needed")
     # (a window bounds the keys a row visits, whatever its sequence's length)
-    ns = int(n_splits) if n_splits else decode_splits(B, nkv, _keys_visited(max_kv_len, window, page),
-                                                      q.device)
+    ns = int(n_splits) if n_splits else decode_splits(
+        B, nkv, _keys_visited(max_kv_len, window, page, keep_first), q.device)
     out = torch.empty_like(q)
     part_o = part_ml = None
     if ns > 1:
@@ -1284,6 +1301,7 @@ def attn_decode_bf16(q, k_pages, v_pages, block_table, *, slots, kv_len, page: i
     a.part_o, a.part_ml = _ptr(part_o), _ptr(part_ml)
     a.n_seqs, a.nq, a.nkv, a.max_pages, a.page = B, nq, nkv, block_table.shape[1], page
     a.window, a.n_splits, a.scale_log2 = int(window or 0), ns, float(scale) * _LOG2E
+    a.keep_first = int(keep_first or 0)
     _set_cap_and_sinks(a, scale, softcap, sinks, nq)
     _check(_fn("attn_decode_bf16", "gb_attn_decode_bf16", "pip")(
         ctypes.addressof(a), D, _stream()), "attn_decode_bf16", 2 if ns > 1 else 1)
@@ -1295,7 +1313,7 @@ class _DecodeTmaArgs(ctypes.Structure):
                 ("part_o", _P), ("part_ml", _P), ("counters", _P), ("error", _P), ("n_seqs", _I),
                 ("nq", _I), ("nkv", _I), ("max_pages", _I), ("window", _I), ("n_splits", _I),
                 ("scale_log2", _F), ("stamps", _P), ("sinks", _P), ("cap_log2", _F),
-                ("cap_inv", _F)]
+                ("cap_inv", _F), ("keep_first", _I)]
 
 
 DECODE_TMA_STAMPS: Optional[torch.Tensor] = None      # int64 [blocks, 12] for tuning, or None
@@ -1349,7 +1367,7 @@ def attn_decode_tma(q, k_pages, v_pages, block_table, *, slots, kv_len, page: in
                     max_kv_len: int, window: Optional[int] = None,
                     n_splits: Optional[int] = None, stages: int = 0,
                     softcap: Optional[float] = None,
-                    sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    sinks: Optional[torch.Tensor] = None, keep_first: int = 0) -> torch.Tensor:
     """Attention of one new token per sequence over its cached keys, the tiles
     brought in by TMA and the splits combined by the block that finishes last (one
     launch).  Heads of 64 or 128, pages of 64 tokens."""
@@ -1366,8 +1384,8 @@ def attn_decode_tma(q, k_pages, v_pages, block_table, *, slots, kv_len, page: in
         raise KernelError("one slot and one length per query row are needed")
     stages = int(stages or DECODE_TMA_STAGES) or (2 if B * nkv < DECODE_TMA_DEEP_PAIRS else 3)
     per_sm = {2: 3, 3: 2, 4: 1}.get(stages, 2) if D == 128 else 3
-    ns = int(n_splits) if n_splits else decode_tma_splits(B, nkv, _keys_visited(max_kv_len, window, page),
-                                                          q.device, per_sm)
+    ns = int(n_splits) if n_splits else decode_tma_splits(
+        B, nkv, _keys_visited(max_kv_len, window, page, keep_first), q.device, per_sm)
     out = torch.empty_like(q)
     a = _DecodeTmaArgs()
     if ns > 1:
@@ -1385,6 +1403,7 @@ def attn_decode_tma(q, k_pages, v_pages, block_table, *, slots, kv_len, page: in
     a.n_seqs, a.nq, a.nkv, a.max_pages = B, nq, nkv, block_table.shape[1]
     a.window, a.n_splits, a.scale_log2 = int(window or 0), ns, float(scale) * _LOG2E
     a.stamps = _ptr(DECODE_TMA_STAMPS)
+    a.keep_first = int(keep_first or 0)
     _set_cap_and_sinks(a, scale, softcap, sinks, nq)
     with torch.cuda.device(q.device):
         _check(_fn("attn_decode_tma", "gb_attn_decode_tma", "pplpiiip")(
@@ -1396,14 +1415,16 @@ def attn_decode_tma(q, k_pages, v_pages, block_table, *, slots, kv_len, page: in
 # ---------------------------------------------------------------- attention dispatch
 def attention(q, k_pages, v_pages, block_table, *, step, page: int, scale: float,
               window: Optional[int] = None, softcap: Optional[float] = None,
-              sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
+              sinks: Optional[torch.Tensor] = None, keep_first: int = 0) -> torch.Tensor:
     """Attention of the step's queries over their sequences' cached keys.
     32-bit tensors take the plain 32-bit kernel; bfloat16 takes the tensor-core
     kernels where they accept the shape and the plain kernel elsewhere.
     ``softcap`` c: scores become c * tanh(score / c); ``sinks`` [nq] float32: one
-    more term exp(sinks[h]) in the denominator of query head h."""
+    more term exp(sinks[h]) in the denominator of query head h; ``keep_first`` F: with a
+    window, key j < F stays visible to every later query (at its own position)."""
     _T, nq, D = q.shape
-    extra = dict(softcap=softcap, sinks=sinks)
+    keep_first = int(keep_first or 0) if window else 0
+    extra = dict(softcap=softcap, sinks=sinks, keep_first=keep_first)
     if q.dtype == torch.bfloat16 and fast_attention_takes(D, nq, k_pages.shape[1], page):
         nkv = k_pages.shape[1]
         if step.decode and attn_decode_tma_takes(D, nq, nkv, page) and (
@@ -1427,7 +1448,7 @@ def attention(q, k_pages, v_pages, block_table, *, step, page: int, scale: float
                                  page=page, scale=scale, window=window, **extra)
     return attn_generic(q, k_pages, v_pages, block_table, token_seq=step.token_seq,
                         token_pos=step.token_pos, slots=step.slots, page=page, scale=scale,
-                        window=window, softcap=softcap, sinks=sinks)
+                        window=window, softcap=softcap, sinks=sinks, keep_first=keep_first)
 
 
 # ---------------------------------------------------------------- gated delta rule
@@ -1766,10 +1787,11 @@ class _MoeArgs(ctypes.Structure):
                 ("offsets", _P), ("perm", _P), ("act", _P), ("out", _P), ("T", _I), ("W", _I),
                 ("F", _I), ("E", _I), ("n_identity", _I), ("top", _I), ("n_groups", _I),
                 ("keep_groups", _I), ("limit", _F), ("slope", _F), ("score_fn", _I),
-                ("weigh_input", _I), ("up_offset", _F)]
+                ("weigh_input", _I), ("up_offset", _F), ("router_bias", _P)]
 
 
 _MOE_COUNTS = {}
+MOE_SCORE_FNS = {"softmax": 0, "sigmoid": 1, "softmax_top": 2}     # the route kernel's codes
 
 
 def _cost_moe(out, x, router_w, correction, w_gate, w_up, w_down, *, top, **k):
@@ -1784,13 +1806,16 @@ def moe_forward(x: torch.Tensor, router_w: torch.Tensor, correction: Optional[to
                 w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, *, top: int,
                 n_identity: int = 0, n_groups: int = 1, keep_groups: int = 1,
                 limit: float = math.inf, slope: float = 1.0, score_fn: str = "softmax",
-                weigh_input: bool = False, up_offset: float = 1.0, want_choice: bool = False):
+                weigh_input: bool = False, up_offset: float = 1.0, want_choice: bool = False,
+                router_bias: Optional[torch.Tensor] = None):
     """A feed-forward of routed experts on rows x [T, W] -> 32-bit partial sums
     [top, T, W], choice j of every token in [j], already weighted; their sum is the
     feed-forward's output.  ``router_w`` [E + n_identity, W] and ``correction`` are
     32-bit; the experts' weights [E, F, W], [E, F, W], [E, W, F] have the type of x.
     The last ``n_identity`` router outputs stand for experts that return their input.
-    ``score_fn`` "sigmoid" scores every output by itself instead of by the softmax;
+    ``score_fn`` "sigmoid" scores every output by itself instead of by the softmax,
+    "softmax_top" lets the logits choose and weighs the chosen by the softmax over their
+    logits alone; ``router_bias`` (32-bit) is added to the logits;
     ``correction`` may be None; ``weigh_input`` multiplies the expert's input, not its
     result, by the weight; an expert is Wd (g sigmoid(slope g) (u + up_offset)) with g
     and u clamped at ``limit``.
@@ -1800,8 +1825,12 @@ def moe_forward(x: torch.Tensor, router_w: torch.Tensor, correction: Optional[to
     _need(router_w, "router weight", torch.float32, 2)
     if correction is not None:
         _need(correction, "score correction", torch.float32, 1)
-    if score_fn not in ("softmax", "sigmoid"):
-        raise KernelError(f"score function '{score_fn}': softmax or sigmoid")
+    if score_fn not in MOE_SCORE_FNS:
+        raise KernelError(f"score function '{score_fn}': one of {sorted(MOE_SCORE_FNS)}")
+    if router_bias is not None:
+        _need(router_bias, "router bias", torch.float32, 1)
+        if router_bias.shape[0] != router_w.shape[0]:
+            raise KernelError("the router's bias and its weight do not fit together")
     for t, nm in ((w_gate, "gate weights"), (w_up, "up weights"), (w_down, "down weights")):
         _need(t, nm, x.dtype, 3)
     E, F = w_gate.shape[0], w_gate.shape[1]
@@ -1829,10 +1858,179 @@ def moe_forward(x: torch.Tensor, router_w: torch.Tensor, correction: Optional[to
     a.offsets, a.perm, a.act, a.out = offsets.data_ptr(), perm.data_ptr(), act.data_ptr(), out.data_ptr()
     a.T, a.W, a.F, a.E, a.n_identity, a.top = T, W, F, E, int(n_identity), int(top)
     a.n_groups, a.keep_groups, a.limit, a.slope = int(n_groups), int(keep_groups), float(limit), float(slope)
-    a.score_fn, a.weigh_input, a.up_offset = int(score_fn == "sigmoid"), int(weigh_input), float(up_offset)
+    a.score_fn, a.weigh_input, a.up_offset = MOE_SCORE_FNS[score_fn], int(weigh_input), float(up_offset)
+    a.router_bias = _ptr(router_bias)
     _check(_fn("moe", f"gb_moe_forward_{_suffix(x.dtype)}", "pp")(ctypes.addressof(a), _stream()),
            "moe_forward", 3)
     return (out, ids, wts) if want_choice else out
+
+
+# ---------------------------------------------------------------- forget-gate linear attention
+class _Hgrn2Args(ctypes.Structure):
+    _fields_ = [("proj", _P), ("ld", _L), ("q_col", _I), ("f_col", _I), ("v_col", _I), ("f_bias", _P),
+                ("lower", _P), ("norm_w", _P), ("cu_q", _P), ("slots", _P), ("state", _P),
+                ("state_stride", _L), ("o", _P), ("y", _P), ("y_ld", _L), ("n_tokens", _I),
+                ("n_seqs", _I), ("H", _I), ("dk", _I), ("dv", _I), ("norm_eps", _F), ("out_scale", _F)]
+
+
+def _cost_hgrn2(out, proj, state, *a, H, dk, dv, **k):
+    """The step's rows once, the states of its sequences read and written (an upper bound:
+    padding sequences store nothing), and per row and head 2 dk dv multiply-adds for the
+    state and as many for the read-out."""
+    T = proj.shape[0]
+    n_seqs = k["slots"].shape[0]
+    return (T * (2 * H * dk + 2 * H * dv) * 4 + _nbytes(out) + 2 * n_seqs * H * dk * dv * 4,
+            4.0 * T * H * dk * dv)
+
+
+@_profiled("hgrn2_forward", _cost_hgrn2)
+def hgrn2_forward(proj: torch.Tensor, state: torch.Tensor, f_bias: torch.Tensor, lower: torch.Tensor,
+                  norm_w: torch.Tensor, *, H: int, dk: int, dv: int, q_col: int, f_col: int,
+                  v_col: int, norm_eps: float, cu_q, slots, dtype: torch.dtype,
+                  out_scale: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Linear attention whose forget gate decides what is written, on the 32-bit sums of a
+    projection ``proj`` [T, ld] whose columns from ``q_col``, ``f_col`` (H dk each) and
+    ``v_col`` (H dv) are this mixer's: q = silu(zq), f = lower + (1 - lower) sigmoid(zf +
+    f_bias); per head S <- diag(f) S + (1 - f) v^T, o = S^T q; y = rmsnorm(o) * norm_w *
+    out_scale in ``dtype``.  ``state`` [slots + 1, H dk dv] (32-bit) is read and updated for
+    the sequences of ``cu_q`` whose slot is not negative.  ``out``: a 2-D view [T, H dv] of a
+    wider row to write into (its row pitch is kept); else a new tensor."""
+    if (proj is None or not proj.is_cuda or proj.dtype != torch.float32 or proj.dim() != 2
+            or proj.stride(1) != 1):
+        raise KernelError("projection sums must be a 32-bit [T, columns] CUDA view with unit stride")
+    T, ld = proj.shape[0], proj.stride(0)
+    for c, n in ((q_col, H * dk), (f_col, H * dk), (v_col, H * dv)):
+        if c < 0 or c + n > proj.shape[1]:
+            raise KernelError(f"columns {c}..{c + n} lie outside the projection's {proj.shape[1]}")
+    _need(state, "state", torch.float32, 2)
+    if state.shape[1] != H * dk * dv:
+        raise KernelError(f"state rows hold {state.shape[1]} floats, expected {H * dk * dv}")
+    for t, nm, n in ((f_bias, "forget bias", H * dk), (lower, "lower bound", H * dk), (norm_w, "norm weight", dv)):
+        _need(t, nm, torch.float32, 1)
+        if t.shape[0] != n:
+            raise KernelError(f"{nm} has {t.shape[0]} elements, expected {n}")
+    _need(cu_q, "cu_q", torch.int32, 1)
+    _need(slots, "slots", torch.int32, 1)
+    if out is None:
+        out = torch.empty((T, H * dv), dtype=dtype, device=proj.device)
+    elif (out.dim() != 2 or tuple(out.shape) != (T, H * dv) or out.dtype != dtype or out.stride(1) != 1
+          or not out.is_cuda):
+        raise KernelError("the output view must be [T, H dv] of the activation type with unit stride")
+    o = torch.empty((T, H, dv), dtype=torch.float32, device=proj.device)
+    a = _Hgrn2Args()
+    a.proj, a.ld, a.q_col, a.f_col, a.v_col = proj.data_ptr(), ld, int(q_col), int(f_col), int(v_col)
+    a.f_bias, a.lower, a.norm_w = f_bias.data_ptr(), lower.data_ptr(), norm_w.data_ptr()
+    a.cu_q, a.slots, a.state, a.state_stride = cu_q.data_ptr(), slots.data_ptr(), state.data_ptr(), state.stride(0)
+    a.o, a.y, a.y_ld = o.data_ptr(), out.data_ptr(), out.stride(0)
+    a.n_tokens, a.n_seqs, a.H, a.dk, a.dv = T, slots.shape[0], int(H), int(dk), int(dv)
+    a.norm_eps, a.out_scale = float(norm_eps), float(out_scale)
+    _check(_fn("hgrn2", f"gb_hgrn2_{_suffix(dtype)}", "pp")(ctypes.addressof(a), _stream()),
+           "hgrn2_forward", 2)
+    return out
+
+
+# ---------------------------------------------------------------- gated sums, depth average, norm
+class _GatedTerm(ctypes.Structure):
+    _fields_ = [("delta", _P), ("parts", _P), ("n_parts", _I), ("part_stride", _L), ("gate", _P),
+                ("gate_ld", _L), ("gate_bias", _P)]
+
+
+class _GatedNormArgs(ctypes.Structure):
+    _fields_ = [("res_in", _P), ("term", _GatedTerm * 2), ("hist", _P), ("hist_stride", _L),
+                ("n_hist", _I), ("avg_w", _P), ("rows", _P), ("norm_w", _P), ("eps", _F),
+                ("res_out", _P), ("y", _P), ("n_rows", _I), ("N", _I)]
+
+
+@_profiled("gated_norm", lambda out, res_in, terms, **k: (
+    _nbytes(res_in, *out, *[t for term in terms for t in term[:2]])
+    + (k.get("n_hist") or 0) * (_nbytes(res_in) if res_in is not None else 0), 0))
+def gated_norm(res_in: Optional[torch.Tensor], terms, *, dtype: torch.dtype,
+               hist: Optional[torch.Tensor] = None, n_hist: int = 0,
+               avg_w: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
+               norm_w: Optional[torch.Tensor] = None, eps: float = 0.0):
+    """X = res_in + sum over up to two ``terms`` (delta, gate logits, gate bias) of
+    sigmoid(gate + bias) * delta (a term without gate is added as it is; delta is [T, N]
+    in ``dtype`` or a stack of 32-bit partial sums [S, T, N]; the gate's logits are a 32-bit
+    2-D view [T, N] whose row pitch is kept); then, with ``hist`` [n, T, N]: X is stored as
+    entry ``n_hist`` and x' = sum_j avg_w[j] hist[j] over j <= n_hist, else x' = X; then
+    y = rmsnorm(x') * norm_w (or x' itself without ``norm_w``) in ``dtype``.  Returns (x', y);
+    x' replaces ``res_in`` in place unless ``rows`` picks rows (then nothing is stored in
+    ``hist`` either).  All sums are 32-bit."""
+    src = res_in
+    a = _GatedNormArgs()
+    if res_in is not None:
+        _need(res_in, "residual", torch.float32, 2)
+    if len(terms) > 2:
+        raise KernelError("at most two gated terms")
+    for i, (delta, gate, bias) in enumerate(terms):
+        if delta is None:
+            continue
+        g = a.term[i]
+        if delta.dim() == 3:
+            _need(delta, "partial sums", torch.float32, 3)
+            g.parts, g.n_parts, g.part_stride = delta.data_ptr(), delta.shape[0], delta.stride(0)
+            shape = tuple(delta.shape[1:])
+        else:
+            _need(delta, "delta", dtype, 2)
+            g.delta, shape = delta.data_ptr(), tuple(delta.shape)
+        if src is None:
+            src = delta[0] if delta.dim() == 3 else delta
+        if shape != tuple(src.shape):
+            raise KernelError(f"a term of {shape} for a stream of {tuple(src.shape)}")
+        if gate is not None:
+            if (gate.dtype != torch.float32 or gate.dim() != 2 or tuple(gate.shape) != shape
+                    or gate.stride(1) != 1 or not gate.is_cuda):
+                raise KernelError("gate logits must be a 32-bit [T, N] view with unit stride")
+            g.gate, g.gate_ld = gate.data_ptr(), gate.stride(0)
+            if bias is not None:
+                _need(bias, "gate bias", torch.float32, 1)
+                g.gate_bias = bias.data_ptr()
+    if src is None:
+        raise KernelError("gated_norm needs a residual or a term")
+    T, N = src.shape
+    if hist is not None:
+        _need(hist, "earlier results", torch.float32, 3)
+        _need(avg_w, "averaging weights", torch.float32, 1)
+        if tuple(hist.shape[1:]) != (T, N) or not 0 <= n_hist < hist.shape[0] or avg_w.shape[0] != n_hist + 1:
+            raise KernelError("the earlier results, their count and the weights do not fit together")
+        a.hist, a.hist_stride, a.n_hist, a.avg_w = hist.data_ptr(), hist.stride(0), int(n_hist), avg_w.data_ptr()
+    if norm_w is not None:
+        _need(norm_w, "norm weight", torch.float32, 1)
+        if norm_w.shape[0] != N:
+            raise KernelError(f"norm weight has {norm_w.shape[0]} elements for rows of {N}")
+    if rows is not None:
+        _need(rows, "row list", torch.int32, 1)
+    n_rows = rows.shape[0] if rows is not None else T
+    res_out = res_in if (rows is None and res_in is not None) else \
+        torch.empty((n_rows, N), dtype=torch.float32, device=src.device)
+    y = torch.empty((n_rows, N), dtype=dtype, device=src.device)
+    a.res_in, a.rows, a.norm_w, a.eps = _ptr(res_in), _ptr(rows), _ptr(norm_w), float(eps)
+    a.res_out, a.y, a.n_rows, a.N = res_out.data_ptr(), y.data_ptr(), n_rows, N
+    _check(_fn("gated_norm", f"gb_gated_norm_{_suffix(dtype)}", "pp")(ctypes.addressof(a), _stream()),
+           "gated_norm")
+    return res_out, y
+
+
+@_profiled("head_gate", lambda out, x, gate, *a, **k: (_nbytes(x) + out.numel() * out.element_size(), 0))
+def head_gate(x: torch.Tensor, gate: Optional[torch.Tensor], v_dim: int, mult: float = 1.0,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t, h * v_dim + d] = x[t, h, d] * sigmoid(gate[t, h]) * mult for d < v_dim, with x
+    [T, heads, Ds] (Ds >= v_dim), ``gate`` a 32-bit 2-D view [T, heads] of logits whose row
+    pitch is kept (None: no gate), and ``out`` a 2-D view [T, heads * v_dim] of a wider row
+    to write into, or None for a new tensor."""
+    _need(x, "heads", ndim=3)
+    T, nq, Ds = x.shape
+    if gate is not None and (gate.dtype != torch.float32 or tuple(gate.shape) != (T, nq) or gate.stride(1) != 1
+                             or not gate.is_cuda):
+        raise KernelError("gate logits must be a 32-bit [T, heads] view with unit stride")
+    if out is None:
+        out = torch.empty((T, nq * v_dim), dtype=x.dtype, device=x.device)
+    elif tuple(out.shape) != (T, nq * v_dim) or out.dtype != x.dtype or out.stride(1) != 1 or not out.is_cuda:
+        raise KernelError("the output view must be [T, heads * v_dim] of x's type with unit stride")
+    _check(_fn("elementwise", f"gb_head_gate_{_suffix(x.dtype)}", "pplpliiiifp")(
+        x.data_ptr(), _ptr(gate), 0 if gate is None else gate.stride(0), out.data_ptr(), out.stride(0),
+        T, nq, Ds, int(v_dim), float(mult), _stream()), "head_gate")
+    return out
 
 
 # ---------------------------------------------------------------- sampling

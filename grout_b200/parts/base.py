@@ -24,7 +24,8 @@ class ParamSpec:
 
     kind: "matrix" (a linear or embedding weight), "vector" (norm weights and
     other small tensors around one), "offset" (biases and other small tensors
-    around zero) or "table" (integer tables, kept as int32).
+    around zero), "fraction" (values inside (0, 1)), "average" (the weights of a
+    weighted sum whose last term leads) or "table" (integer tables, kept as int32).
     The loader keeps bfloat16 as bfloat16 and 32-bit as 32-bit for every kind;
     only the true 32-bit path widens, and only half precision is converted.
     """

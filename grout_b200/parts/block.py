@@ -15,6 +15,7 @@ from typing import Dict
 from typing import Optional
 
 from .base import BuildContext, ParamSpec, Part, PartSpec, build_part, register_part
+from .linear import Linear
 from .norm import Contribution, stream_add
 
 
@@ -175,3 +176,80 @@ class PostNormBlock(Block):
             return res, a
         res, x = stream_add(res, a, self.ctx.dtype)
         return res, Contribution(self.feedforward.forward(x, step), self.norm2, scale=self.scale2)
+
+
+@register_part("block", "parallel")
+class ParallelBlock(Block):
+    """One norm, and both sublayers read its output side by side:
+
+        h = norm1(x);   x += gate1 * mixer(h) + gate2 * feedforward(h)
+
+    The feed-forward's term is absent when the layer has none.  With ``gated`` each
+    sublayer's result is multiplied element by element by sigmoid(W h + b) ("gated
+    residual"), W and b being the tensors ``gate1`` / ``gate2`` (local names; the bias is
+    the name + ``bias_suffix``) under the layer's prefix; both gates' logits come from one
+    product with 32-bit sums.  The sublayers' results leave as a tuple of
+    ``Contribution``s, so the sum into the stream is done by the kernel of whoever reads
+    the stream next (the next layer's norm, or the model's last one)."""
+
+    def __init__(self, ctx: BuildContext, norm1: PartSpec, mixer: PartSpec,
+                 feedforward: Optional[PartSpec] = None, gated: bool = False,
+                 gate1: str = "rg1", gate2: str = "rg2", bias_suffix: str = ".b"):
+        super().__init__(ctx)
+        self.norm1 = build_part("norm", norm1, ctx)
+        self.mixer = build_part("mixer", mixer, ctx)
+        self.feedforward = build_part("feedforward", feedforward, ctx) if feedforward else None
+        self.gated = bool(gated)
+        self.gate_names = (gate1, gate2 if feedforward else None) if self.gated else (None, None)
+        self.bias_suffix = bias_suffix
+        self.width = self.norm1.dim
+        self.gates = None
+        self.gate_bias = (None, None)
+
+    def named_parts(self) -> Dict[str, Part]:
+        roles = ("norm1", "mixer", "feedforward")
+        return {r: getattr(self, r) for r in roles if getattr(self, r) is not None}
+
+    def children(self):
+        return tuple(self.named_parts().values())
+
+    def param_specs(self):
+        specs = {}
+        for n in self.gate_names:
+            if n:
+                specs[n] = ParamSpec((self.width, self.width))
+                specs[n + self.bias_suffix] = ParamSpec((self.width,), "offset")
+        return specs
+
+    def load(self, params):
+        import torch
+        names = [n for n in self.gate_names if n]
+        ws = [params[n] for n in names]
+        if len({w.dtype for w in ws}) > 1:
+            raise ValueError("the two residual gates must be stored in one dtype to be fused")
+        self.gates = Linear(torch.cat(ws, dim=0) if len(ws) > 1 else ws[0], self.ctx.products)
+        # 32-bit whatever the checkpoint stores: the sum into the stream is 32-bit
+        self.gate_bias = tuple(params[n + self.bias_suffix].float().contiguous() if n else None
+                               for n in self.gate_names)
+
+    def kernel_modules(self):
+        return ("gated_norm",) + (self.gates.kernel_modules() if self.gates else ())
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def captures_prompts(self):
+        return True
+
+    def forward(self, res, pending, step, cache):
+        import torch
+        res, h = self.norm1.add_norm(res, pending)
+        W = self.width
+        logits = self.gates(h, out_dtype=torch.float32) if self.gated else None
+        a = self.mixer.forward(h, step, cache)
+        terms = [Contribution(a, gate=logits[:, :W] if self.gated else None, gate_bias=self.gate_bias[0])]
+        if self.feedforward is not None:
+            m = self.feedforward.forward(h, step)
+            terms.append(Contribution(m, gate=logits[:, W:2 * W] if self.gated else None,
+                                      gate_bias=self.gate_bias[1]))
+        return res, tuple(terms)

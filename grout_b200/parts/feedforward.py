@@ -181,7 +181,9 @@ class RoutedExperts(FeedForward):
     """``n_experts`` small gated feed-forwards of which every token uses ``top``.
 
         z = Wr x (32-bit), s = softmax(z) over all n_experts + n_identity outputs
-        (``score_fn`` "sigmoid": s = sigmoid(z), every output by itself)
+        (``score_fn`` "sigmoid": s = sigmoid(z), every output by itself; "softmax_top": the
+        logits z themselves choose, and the chosen weigh in with the softmax over their own
+        logits alone; ``router_bias``: z = Wr x + b, b the tensor ``router_bias_name``)
         c = s + correction (``correction`` False: there is none, c = s);  the outputs form ``n_groups`` equal groups of neighbours,
         a group's score is its largest c, only outputs of the ``keep_groups`` best
         groups can be chosen; the ``top`` largest c are chosen and weigh in with s
@@ -200,16 +202,19 @@ class RoutedExperts(FeedForward):
     def __init__(self, ctx: BuildContext, hidden: int, intermediate: int, n_experts: int, top: int,
                  limit: Optional[float], gate_slope: float, n_identity: int = 0, n_groups: int = 1,
                  keep_groups: int = 1, score_fn: str = "softmax", correction: bool = True,
-                 weigh_input: bool = False, up_offset: float = 1.0):
+                 weigh_input: bool = False, up_offset: float = 1.0, router_bias: bool = False,
+                 router_bias_name: str = "router.b"):
         super().__init__(ctx)
         self.hidden, self.intermediate = int(hidden), int(intermediate)
         self.E, self.n_identity, self.top = int(n_experts), int(n_identity), int(top)
         self.n_groups, self.keep_groups = int(n_groups), int(keep_groups)
         self.limit = math.inf if limit is None else float(limit)
         self.gate_slope, self.up_offset = float(gate_slope), float(up_offset)
-        if score_fn not in ("softmax", "sigmoid"):
-            raise ValueError(f"score function '{score_fn}': softmax or sigmoid")
+        if score_fn not in ops.MOE_SCORE_FNS:
+            raise ValueError(f"score function '{score_fn}': one of {sorted(ops.MOE_SCORE_FNS)}")
         self.score_fn, self.has_correction, self.weigh_input = score_fn, bool(correction), bool(weigh_input)
+        self.has_router_bias, self.router_bias_name = bool(router_bias), router_bias_name
+        self.router_b = None
         n_all = self.E + self.n_identity
         if n_all % self.n_groups or not 1 <= self.keep_groups <= self.n_groups:
             raise ValueError(f"{n_all} router outputs do not form {self.n_groups} equal groups "
@@ -223,6 +228,8 @@ class RoutedExperts(FeedForward):
         specs = {"router": ParamSpec((n_all, self.hidden))}
         if self.has_correction:
             specs["correction"] = ParamSpec((n_all,), "offset")
+        if self.has_router_bias:
+            specs[self.router_bias_name] = ParamSpec((n_all,), "offset")
         for j in range(self.E):
             specs[f"e{j}.gate"] = ParamSpec((self.intermediate, self.hidden))
             specs[f"e{j}.up"] = ParamSpec((self.intermediate, self.hidden))
@@ -233,6 +240,8 @@ class RoutedExperts(FeedForward):
         # the router is 32-bit whatever the checkpoint stores
         self.router_w = params["router"].float().contiguous()
         self.correction = params["correction"].float().contiguous() if self.has_correction else None
+        self.router_b = (params[self.router_bias_name].float().contiguous()
+                         if self.has_router_bias else None)
         stack = lambda what: torch.stack([params[f"e{j}.{what}"] for j in range(self.E)]).to(
             self.ctx.dtype).contiguous()
         self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
@@ -248,4 +257,5 @@ class RoutedExperts(FeedForward):
                                self.w_down, top=self.top, n_identity=self.n_identity,
                                n_groups=self.n_groups, keep_groups=self.keep_groups,
                                limit=self.limit, slope=self.gate_slope, score_fn=self.score_fn,
-                               weigh_input=self.weigh_input, up_offset=self.up_offset)
+                               weigh_input=self.weigh_input, up_offset=self.up_offset,
+                               router_bias=self.router_b)

@@ -46,9 +46,9 @@ class TokenEmbedding(Embedding):
     def captures_prompts(self):
         return True
 
-    def forward(self, tokens, step):
+    def forward(self, tokens, step, out=None):
         if self.scale is not None:
-            return ops.embed_scaled(self.weight, tokens, self.scale)
+            return ops.embed_scaled(self.weight, tokens, self.scale, out=out)
         x = ops.embed(self.weight, tokens)
         return ops.cast(x, self.ctx.dtype) if x.dtype != self.ctx.dtype else x
 

@@ -21,7 +21,7 @@ from typing import Optional
 
 import torch
 
-from ..cache.spec import KVSpec
+from ..cache.spec import KVSpec, SideBySideSpec
 from ..kernels import ops
 from .base import BuildContext, ParamSpec, Part, PartSpec, build_part, register_part
 from .linear import Linear
@@ -64,12 +64,23 @@ class GQAAttention(Mixer):
     size than queries and keys; the cache, the queries and the attention's output
     are then as wide as the larger of the two, filled up with zeros, and the o
     projection's columns likewise, so that every attention kernel serves.
-    ``names`` replaces local tensor names (keys: q, k, v, o, q_norm, k_norm, sink).
+    ``keep_first`` F: with a window, the sequence's first F tokens stay visible to every
+    later query, at their own positions (their pages are kept).  ``head_gate``: every
+    head's output is multiplied by sigmoid(Wg h)_head, one number a head (tensor ``g``
+    [heads, hidden]; 32-bit sums, 32-bit sigmoid), before the o projection.  A rotation
+    of neighbouring pairs (``rotary_interleaved``) is folded into the q/k kernel as the
+    half-split one is.
+    ``names`` replaces local tensor names (keys: q, k, v, o, q_norm, k_norm, sink, g).
+
+    The mixer can run beside another one on the same input (``SideBySide``): it then names
+    the rows whose 32-bit products with the input it needs (``side_weight``: the head gate's),
+    leaves the o projection's input in a view it is given (``inner``) and hands out its o
+    weight (``out_weight``) instead of multiplying by it.
     """
 
     NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight",
              "o": "o_proj.weight", "q_norm": "q_norm.weight", "k_norm": "k_norm.weight",
-             "sink": "sink"}
+             "sink": "sink", "g": "g"}
 
     def __init__(self, ctx: BuildContext, hidden: int, n_heads: int, n_kv_heads: int,
                  head_dim: int, position: PartSpec, qk_norm_eps: Optional[float] = None,
@@ -77,8 +88,12 @@ class GQAAttention(Mixer):
                  shares_kv: bool = False, softcap: Optional[float] = None, sinks: bool = False,
                  values_are_keys: bool = False, names: Optional[dict] = None,
                  v_head_dim: Optional[int] = None, q_temp: Optional[tuple] = None,
-                 sink_logit: Optional[float] = None):
+                 sink_logit: Optional[float] = None, keep_first: int = 0, head_gate: bool = False):
         super().__init__(ctx)
+        self.keep_first = int(keep_first or 0) if window else 0
+        self.head_gate = bool(head_gate)
+        self.beside = False          # set by a SideBySide parent before load
+        self.g = self.g_w = self.o_w = None
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads cannot share {n_kv_heads} kv heads")
         self.hidden, self.nq, self.nkv, self.D = int(hidden), int(n_heads), int(n_kv_heads), int(head_dim)
@@ -131,6 +146,8 @@ class GQAAttention(Mixer):
                 specs[nm["k_norm"]] = ParamSpec((D,), "vector")
         if self.has_sinks:
             specs[nm["sink"]] = ParamSpec((nq,), "offset")
+        if self.head_gate:
+            specs[nm["g"]] = ParamSpec((nq, H))
         return specs
 
     def load(self, params):
@@ -142,11 +159,17 @@ class GQAAttention(Mixer):
             raise ValueError("q, k and v projections must be stored in one dtype to be fused")
         self.qkv = Linear(torch.cat(ws, dim=0) if len(ws) > 1 else ws[0], self.ctx.products)
         o = params[nm["o"]]
-        if self.Ds != self.Dv:      # zero columns where the attention's output is filled up
-            wide = o.new_zeros((self.hidden, self.nq, self.Ds))
-            wide[:, :, :self.Dv] = o.view(self.hidden, self.nq, self.Dv)
-            o = wide.view(self.hidden, self.nq * self.Ds)
-        self.o = Linear(o, self.ctx.products)
+        if self.beside:             # the parent multiplies: by one weight for all its mixers
+            self.o_w, self.g_w = o, (params[nm["g"]] if self.head_gate else None)
+        elif self.head_gate:        # the gate's kernel also drops what fills up a head
+            self.o = Linear(o, self.ctx.products)
+            self.g = Linear(params[nm["g"]], self.ctx.products)
+        else:
+            if self.Ds != self.Dv:      # zero columns where the attention's output is filled up
+                wide = o.new_zeros((self.hidden, self.nq, self.Ds))
+                wide[:, :, :self.Dv] = o.view(self.hidden, self.nq, self.Dv)
+                o = wide.view(self.hidden, self.nq * self.Ds)
+            self.o = Linear(o, self.ctx.products)
         if self.sink_logit is not None:
             self.sink = torch.full((self.nq,), self.sink_logit, dtype=torch.float32, device=o.device)
         if self.qk_norm_eps is not None:
@@ -157,13 +180,38 @@ class GQAAttention(Mixer):
             self.sink = params[nm["sink"]].float().contiguous()
 
     def kernel_modules(self):
-        mods = ("qk_prepare", "attn_generic") + self.qkv.kernel_modules() + self.o.kernel_modules()
+        mods = ("qk_prepare", "attn_generic") + self.qkv.kernel_modules()
+        mods += self.o.kernel_modules() if self.o else ()
+        if self.head_gate or self.beside:
+            mods += ("elementwise",)
         if self.ctx.dtype == torch.bfloat16:
             mods += ops.fast_attention_modules(self.Ds, self.nq, self.nkv)
         return mods
 
     def cache_spec(self):
-        return None if self.shares_kv else KVSpec(self.nkv, self.Ds, self.window)
+        if self.shares_kv:
+            return None
+        if self.keep_first:
+            return KVSpec(self.nkv, self.Ds, self.window, keep_first=self.keep_first)
+        return KVSpec(self.nkv, self.Ds, self.window)
+
+    # -- beside another mixer ------------------------------------------------
+    @property
+    def inner_width(self) -> int:
+        return self.nq * self.Dv
+
+    def side_weight(self):
+        return self.g_w
+
+    def out_weight(self):
+        return self.o_w
+
+    def inner(self, x, step, cache, sums=None, out=None, mult: float = 1.0):
+        """The o projection's input [T, heads * v_head_dim], times ``mult``: the heads'
+        outputs under their gates (``sums``: the 32-bit products of ``side_weight`` with
+        x), written into ``out`` when given."""
+        attn = self._attend(x, step, cache)
+        return ops.head_gate(attn, sums if self.head_gate else None, self.Dv, mult, out)
 
     def captures_prompts(self):
         # an encoding with arithmetic of its own runs between two kernels here and
@@ -171,6 +219,15 @@ class GQAAttention(Mixer):
         return True
 
     def forward(self, x, step, cache):
+        T = x.shape[0]
+        if self.head_gate:
+            y = self.inner(x, step, cache, self.g(x, out_dtype=torch.float32))
+            return self.o(y, partial_ok=True)
+        attn = self._attend(x, step, cache)
+        return self.o(attn.view(T, self.nq * self.Ds), partial_ok=True)
+
+    def _attend(self, x, step, cache):
+        """The heads' outputs [T, heads, Ds] (keys and values of the step's rows stored)."""
         T = x.shape[0]
         rot = self.position.rotary()
         if cache is None or (cache.spec.n_kv_heads, cache.spec.head_dim) != (self.nkv, self.Ds):
@@ -187,13 +244,13 @@ class GQAAttention(Mixer):
                                   eps=self.qk_norm_eps or 0.0,
                                   inv_freq=rot.inv_freq if rot else None,
                                   rot_dim=rot.rot_dim if rot else 0, token_seq=step.token_seq,
-                                  token_pos=step.token_pos, slots=step.slots, q_temp=self.q_temp)
+                                  token_pos=step.token_pos, slots=step.slots, q_temp=self.q_temp,
+                                  interleaved=bool(rot and rot.interleaved))
             if rot is None:
                 q, _k = self.position.apply_qk(q, q[:, :0], step.token_pos)
-            attn = ops.attention(q.contiguous(), cache.k_pages, cache.v_pages, cache.block_table,
+            return ops.attention(q.contiguous(), cache.k_pages, cache.v_pages, cache.block_table,
                                  step=step, page=cache.page, scale=self.scale, window=self.window,
-                                 softcap=self.softcap, sinks=self.sink)
-            return self.o(attn.view(T, self.nq * self.Ds), partial_ok=True)
+                                 softcap=self.softcap, sinks=self.sink, keep_first=self.keep_first)
         common = dict(q_w=self.q_norm_w, k_w=self.k_norm_w, eps=self.qk_norm_eps or 0.0,
                       values_are_keys=self.values_are_keys, token_seq=step.token_seq, token_pos=step.token_pos, slots=step.slots)
         if fused:
@@ -202,7 +259,8 @@ class GQAAttention(Mixer):
                                   rot_dim=rot.rot_dim if rot else 0,
                                   block_table=cache.block_table, k_pages=cache.k_pages,
                                   v_pages=cache.v_pages, page=cache.page, v_dim=self.Dv,
-                                  q_temp=self.q_temp, **common)
+                                  q_temp=self.q_temp, interleaved=bool(rot and rot.interleaved),
+                                  **common)
         else:
             # a position encoding with its own arithmetic: normalise, hand q and k
             # over, then store
@@ -214,10 +272,87 @@ class GQAAttention(Mixer):
                          slots=step.slots, block_table=cache.block_table, k_pages=cache.k_pages,
                          v_pages=cache.v_pages, page=cache.page)
             q = q.contiguous()
-        attn = ops.attention(q, cache.k_pages, cache.v_pages, cache.block_table, step=step,
+        return ops.attention(q, cache.k_pages, cache.v_pages, cache.block_table, step=step,
                              page=cache.page, scale=self.scale, window=self.window,
-                             softcap=self.softcap, sinks=self.sink)
-        return self.o(attn.view(T, self.nq * self.Ds), partial_ok=True)
+                             softcap=self.softcap, sinks=self.sink, keep_first=self.keep_first)
+
+
+@register_part("mixer", "side_by_side")
+class SideBySide(Mixer):
+    """Mixers that read the same input side by side; the result is the sum of theirs,
+    each times a constant:  y = sum_i scale_i * mixer_i(h).
+
+    ``mixers`` is a tuple of (name, PartSpec, scale); a mixer's tensors lie under
+    ``<name>.``.  Each mixer must be able to run beside another (``side_weight``,
+    ``inner``, ``out_weight``, ``inner_width``: see ``GQAAttention``): the rows whose 32-bit
+    products with h the mixers need are one product, every mixer leaves the input of its
+    output projection, already times its constant, in its part of one wide row, and the
+    output projections are one product over that row.  The layer's cache need is the
+    tuple of the mixers' needs (``SideBySideSpec``)."""
+
+    def __init__(self, ctx: BuildContext, hidden: int, mixers):
+        super().__init__(ctx)
+        self.hidden = int(hidden)
+        self.names = [m[0] for m in mixers]
+        self.scales = [float(m[2]) for m in mixers]
+        self.parts = [build_part("mixer", m[1], ctx) for m in mixers]
+        if len(set(self.names)) != len(self.names) or not self.parts:
+            raise ValueError("mixers side by side need names of their own")
+        for n, p in zip(self.names, self.parts):
+            if not all(hasattr(p, a) for a in ("side_weight", "inner", "out_weight", "inner_width")):
+                raise ValueError(f"mixer '{n}' ({type(p).__name__}) cannot run beside another")
+            p.beside = True
+        self.side = self.o = None
+        self.side_cols = []           # per mixer (first column, count) in the side product
+        self.inner_cols = []          # per mixer (first column, count) in the wide row
+
+    def children(self):
+        return tuple(self.parts)
+
+    def param_specs(self):
+        return {f"{n}.{local}": spec for n, p in zip(self.names, self.parts)
+                for local, spec in p.param_specs().items()}
+
+    def load(self, params):
+        side, outs, at_s, at_i = [], [], 0, 0
+        self.side_cols, self.inner_cols = [], []
+        for n, p in zip(self.names, self.parts):
+            p.load({local: params[f"{n}.{local}"] for local in p.param_specs()})
+            w = p.side_weight()
+            self.side_cols.append((at_s, 0 if w is None else w.shape[0]))
+            if w is not None:
+                side.append(w)
+                at_s += w.shape[0]
+            self.inner_cols.append((at_i, p.inner_width))
+            outs.append(p.out_weight())
+            at_i += p.inner_width
+        if len({w.dtype for w in side + outs}) != 1:
+            raise ValueError("mixers side by side must be stored in one dtype to be fused")
+        self.side = Linear(torch.cat(side, dim=0), self.ctx.products) if side else None
+        self.o = Linear(torch.cat(outs, dim=1), self.ctx.products)
+        for p in self.parts:          # the fused copies serve from here on
+            p.o_w = p.g_w = p.side_w = None
+
+    def kernel_modules(self):
+        mods = self.o.kernel_modules() if self.o else ()
+        return mods + (self.side.kernel_modules() if self.side else ())
+
+    def cache_spec(self):
+        return SideBySideSpec(tuple(p.cache_spec() for p in self.parts))
+
+    def captures_prompts(self):
+        return True
+
+    def forward(self, x, step, cache):
+        if not isinstance(cache, tuple) or len(cache) != len(self.parts):
+            raise ValueError(f"{len(self.parts)} mixers side by side were given the cache {cache!r}")
+        T = x.shape[0]
+        sums = self.side(x, out_dtype=torch.float32) if self.side is not None else None
+        wide = torch.empty((T, self.o.in_features), dtype=self.ctx.dtype, device=x.device)
+        for p, view, scale, (s0, sn), (i0, n) in zip(self.parts, cache, self.scales, self.side_cols,
+                                                     self.inner_cols):
+            p.inner(x, step, view, sums[:, s0:s0 + sn] if sn else None, wide[:, i0:i0 + n], scale)
+        return self.o(wide, partial_ok=True)
 
 
 @register_part("mixer", "latent_attention")

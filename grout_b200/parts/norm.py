@@ -43,6 +43,11 @@ class Contribution:
     mult: float = 1.0
     offset: Optional[torch.Tensor] = None
     scale: Optional[torch.Tensor] = None
+    #: a gated residual: ``delta`` is multiplied element by element by
+    #: sigmoid(gate + gate_bias); ``gate`` is a 32-bit [T, N] view of logits (it may be
+    #: part of a wider row), ``gate_bias`` a 32-bit vector [N] or None
+    gate: Optional[torch.Tensor] = None
+    gate_bias: Optional[torch.Tensor] = None
 
     def resolved(self) -> Optional[torch.Tensor]:
         """The contribution as one 32-bit tensor [T, N] (step by step, for norms
@@ -57,9 +62,54 @@ class Contribution:
             d = d.float() * self.mult if self.mult != 1.0 else d.float()
             if self.scale is not None:
                 d = d * self.scale.float()[None, :]
+            if self.gate is not None:
+                g = self.gate.float()
+                d = d * torch.sigmoid(g if self.gate_bias is None else g + self.gate_bias.float()[None, :])
         if self.offset is not None:
             d = self.offset.float()[None, :] if d is None else d + self.offset.float()[None, :]
         return d
+
+
+@dataclass
+class Averaged:
+    """What a model with a depth-averaged stream hands to the next norm: the layer's
+    contributions ``terms`` (a tensor, a ``Contribution`` or a tuple of them; sublayers
+    that run side by side leave one each) are still to be added to the stream, which
+    gives the layer's result X; X becomes entry ``index`` of ``history`` [n, T, N]
+    (32-bit: the embedding's output and every earlier layer's result lie before it), and
+    the stream that goes on is sum_j weights[j] * history[j], j = 0 .. index."""
+    terms: object
+    history: torch.Tensor
+    index: int
+    weights: torch.Tensor          # 32-bit [index + 1]
+
+    def resolve(self, res: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Step by step, for norms without a kernel that takes all of it: the new stream
+        (of ``rows`` only, when given)."""
+        x = residual_add(res, resolve_terms(self.terms))
+        self.history[self.index].copy_(x)
+        hist = self.history[:self.index + 1]
+        if rows is not None:
+            hist = hist.index_select(1, rows.long())
+        return (self.weights.float()[:, None, None] * hist).sum(dim=0)
+
+
+def as_terms(pending):
+    """``pending`` as a tuple of ``Contribution``s (tensors are wrapped, None is dropped)."""
+    if pending is None:
+        return ()
+    items = pending if isinstance(pending, (tuple, list)) else (pending,)
+    return tuple(p if isinstance(p, Contribution) else Contribution(p) for p in items if p is not None)
+
+
+def resolve_terms(pending) -> Optional[torch.Tensor]:
+    """The sum of all pending contributions as one 32-bit tensor (None: nothing)."""
+    total = None
+    for c in as_terms(pending):
+        d = c.resolved()
+        if d is not None:
+            total = d if total is None else total + d
+    return total
 
 
 def with_offset(pending, offset: torch.Tensor) -> Contribution:
@@ -80,8 +130,11 @@ class Norm(Part):
 
     def add_norm(self, res: Optional[torch.Tensor], delta: Optional[torch.Tensor],
                  rows: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
-        if isinstance(delta, Contribution):
-            delta = delta.resolved()
+        if isinstance(delta, Averaged):
+            res, delta = delta.resolve(res, rows), None
+            return res, self.forward(ops.cast(res, self.ctx.dtype))
+        if isinstance(delta, (Contribution, tuple, list)):
+            delta = resolve_terms(delta)
         res = residual_add(res, delta, rows)
         return res, self.forward(ops.cast(res, self.ctx.dtype))
 
@@ -107,17 +160,22 @@ class RMSNorm(Norm):
     """y = x / sqrt(mean(x^2) + eps) * w; the weight multiplies as it is
     (src/kernels.rs:316-341, src/training.rs:233-238)."""
 
-    def __init__(self, ctx: BuildContext, dim: int, eps: float, name: str = "weight"):
+    def __init__(self, ctx: BuildContext, dim: int, eps: float, name: str = "weight",
+                 unit_offset: bool = False):
+        """``unit_offset``: the tensor is stored around zero and the norm multiplies by
+        1 + w (the sum is taken in 32-bit at load)."""
         super().__init__(ctx)
         self.dim, self.eps, self.name = int(dim), float(eps), name
+        self.unit_offset = bool(unit_offset)
         self.weight = None
         self._weight32 = None
 
     def param_specs(self):
-        return {self.name: ParamSpec((self.dim,), "vector")}
+        return {self.name: ParamSpec((self.dim,), "offset" if self.unit_offset else "vector")}
 
     def load(self, params):
-        self.weight = params[self.name].contiguous()
+        w = params[self.name]
+        self.weight = (1.0 + w.float()).contiguous() if self.unit_offset else w.contiguous()
         self._weight32 = None
 
     def weight32(self) -> torch.Tensor:
@@ -125,9 +183,6 @@ class RMSNorm(Norm):
         if self._weight32 is None:
             self._weight32 = self.weight.float().contiguous()
         return self._weight32
-
-    def kernel_modules(self):
-        return ("norm",)
 
     def captures_prompts(self):
         return True
@@ -137,13 +192,35 @@ class RMSNorm(Norm):
                                   write_res=False)
         return y
 
+    def kernel_modules(self):
+        return ("norm",)
+
     def add_norm(self, res, delta, rows=None):
+        if isinstance(delta, (Averaged, tuple, list)) or (isinstance(delta, Contribution)
+                                                          and delta.gate is not None):
+            return self._add_gated(res, delta, rows)
         if isinstance(delta, Contribution):
             if _one_kernel(delta):
                 return _add_contribution(res, delta, self.ctx.dtype, rows, self)
             # resolved step by step, added in 32-bit
             res, delta = residual_add(res, delta.resolved()), None
         return ops.add_rmsnorm(res, delta, self.weight, self.eps, dtype=self.ctx.dtype, rows=rows)
+
+    def _add_gated(self, res, pending, rows):
+        """Gated contributions of sublayers that ran side by side and, for a model with a
+        depth-averaged stream, the average over the earlier layers' results, in the one
+        kernel that also normalises (``ops.gated_norm``).  Contributions that carry more
+        than a gate (a norm, a factor, a vector of their own) are resolved first."""
+        avg = pending if isinstance(pending, Averaged) else None
+        terms = as_terms(avg.terms if avg else pending)
+        plain = all(c.norm is None and c.mult == 1.0 and c.offset is None and c.scale is None
+                    for c in terms)
+        if not plain or len(terms) > 2:
+            res, terms = residual_add(res, resolve_terms(terms)), ()
+        return ops.gated_norm(res, [(c.delta, c.gate, c.gate_bias) for c in terms],
+                              dtype=self.ctx.dtype, hist=avg.history if avg else None,
+                              n_hist=avg.index if avg else 0, avg_w=avg.weights if avg else None,
+                              rows=rows, norm_w=self.weight32(), eps=self.eps)
 
 
 def _one_kernel(c: Contribution) -> bool:

@@ -15,6 +15,10 @@ needs them, new parts.
   ``name`` (declared in ``ModelPlan.stream_vectors``) to every row of the
   residual stream right before the entry's layer runs: what a model that goes
   through a run of layers several times adds in front of each pass.
+  ``average`` = a tensor's name: the stream that goes on after the entry is a learned
+  weighted sum over the embedding's output and the results of all entries up to this one
+  ("depth-weighted average"); entry k's tensor holds k + 2 weights, the embedding's first.
+  Either every entry of a schedule has one or none has.
 """
 from __future__ import annotations
 
@@ -36,6 +40,7 @@ class ScheduleEntry:
     layer: int
     cache_of: Optional[int] = None        # schedule index whose cache this entry uses
     add: Optional[Tuple[str, int]] = None # (stream vector's tensor name, row) added before it runs
+    average: Optional[str] = None         # tensor [index + 2]: weights of the depth average behind it
 
 
 @dataclass(frozen=True)
@@ -58,6 +63,9 @@ class ModelPlan:
     def validate(self) -> None:
         n = len(self.layers)
         vectors = dict(self.stream_vectors)
+        averaged = [e.average is not None for e in self.schedule]
+        if any(averaged) and not all(averaged):
+            raise ValueError("a depth-averaged stream needs weights behind every schedule entry")
         for i, e in enumerate(self.schedule):
             if e.add is not None and (e.add[0] not in vectors or
                                       not 0 <= e.add[1] < vectors[e.add[0]][0]):

@@ -106,9 +106,9 @@ class RotaryHalfSplit(PositionEncoding):
 @register_part("position", "rotary_interleaved")
 class RotaryInterleaved(RotaryHalfSplit):
     """The same rotation with neighbours as pairs: element 2j goes with element
-    2j + 1, j < rot_dim / 2, and the pair turns by pos * inv_freq[j].  The kernels of
-    ``gqa_attention`` rotate half-split pairs only; the mixers that take this
-    encoding (``latent_attention``) rotate in a kernel of their own."""
+    2j + 1, j < rot_dim / 2, and the pair turns by pos * inv_freq[j].  ``gqa_attention``
+    folds it into its q/k kernel as it does the half-split rotation;
+    ``latent_attention`` rotates in a kernel of its own."""
 
     def __init__(self, ctx: BuildContext, head_dim: int, theta: float,
                  rot_dim: Optional[int] = None, scaling: Optional[dict] = None,

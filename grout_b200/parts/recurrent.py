@@ -260,3 +260,96 @@ class GatedLinearRecurrence(Mixer):
                               cu_q=step.cu_q, slots=step.slots, dtype=self.ctx.dtype,
                               max_rows=step.max_q_len)
         return self.o(y, partial_ok=True)
+
+
+@register_part("mixer", "forget_gate_attention")
+class ForgetGateAttention(Mixer):
+    """Linear attention in which the forget gate also decides what is written (HGRN2).
+    With h the mixer's input,
+
+        q = silu(Wq h)  (n_heads x key_dim),   v = Wv h  (n_heads x value_dim)
+        f = low + (1 - low) * sigmoid(Wf h + bf)      per head and channel; ``low`` is a learned
+                                                      lower bound of the gate, inside [0, 1)
+        S <- diag(f) S + (1 - f) v^T;   o = S^T q     per head: there is no key, 1 - f stands
+                                                      where one would, and no other scale
+        y = Wo [ o / sqrt(mean(o^2) + norm_eps) * w ] the norm per head over value_dim, its
+                                                      weight w [value_dim] shared by the heads
+
+    S [key_dim, value_dim] starts at zero and is kept per sequence in 32-bit.  The three
+    projections are one product that leaves 32-bit sums; all that follows up to y is 32-bit
+    whatever the activation type.  ``names`` replaces local tensor names (keys q, f, f_bias,
+    lower, v, norm, o).  The mixer can run beside another one (``SideBySide``)."""
+
+    NAMES = {"q": "q", "f": "f", "f_bias": "f.b", "lower": "lower", "v": "v", "norm": "norm", "o": "o"}
+
+    def __init__(self, ctx: BuildContext, hidden: int, n_heads: int, key_dim: int, value_dim: int,
+                 norm_eps: float, names=None):
+        super().__init__(ctx)
+        self.hidden, self.H, self.dk, self.dv = int(hidden), int(n_heads), int(key_dim), int(value_dim)
+        self.norm_eps = float(norm_eps)
+        self.names = dict(self.NAMES, **(names or {}))
+        self.beside = False          # set by a SideBySide parent before load
+        self.proj = self.o = self.side_w = self.o_w = None
+        self.f_bias = self.lower = self.norm_w = None
+
+    def param_specs(self):
+        W, H, dk, dv, nm = self.hidden, self.H, self.dk, self.dv, self.names
+        return {nm["q"]: ParamSpec((H * dk, W)), nm["f"]: ParamSpec((H * dk, W)),
+                nm["f_bias"]: ParamSpec((H * dk,), "offset"), nm["lower"]: ParamSpec((H * dk,), "fraction"),
+                nm["v"]: ParamSpec((H * dv, W)), nm["norm"]: ParamSpec((dv,), "vector"),
+                nm["o"]: ParamSpec((W, H * dv))}
+
+    def load(self, params):
+        nm = self.names
+        ws = [params[nm[k]] for k in ("q", "f", "v")]
+        if len({w.dtype for w in ws}) != 1:
+            raise ValueError("the projections of one mixer must be stored in one dtype to be fused")
+        side = torch.cat(ws, dim=0)
+        if self.beside:              # the parent multiplies: one product for all its mixers
+            self.side_w, self.o_w = side, params[nm["o"]]
+        else:
+            self.proj = Linear(side, self.ctx.products)
+            self.o = Linear(params[nm["o"]], self.ctx.products)
+        # what enters the recurrence is 32-bit whatever the checkpoint stores
+        f32 = lambda t: t.float().contiguous()
+        self.f_bias, self.lower = f32(params[nm["f_bias"]]), f32(params[nm["lower"]])
+        self.norm_w = f32(params[nm["norm"]])
+
+    def kernel_modules(self):
+        mods = ("hgrn2",)
+        for lin in (self.proj, self.o):
+            mods += lin.kernel_modules() if lin else ()
+        return mods
+
+    def cache_spec(self):
+        return StateSpec((self.H * self.dk * self.dv,), torch.float32)
+
+    def captures_prompts(self):
+        return True
+
+    # -- beside another mixer ------------------------------------------------
+    @property
+    def inner_width(self) -> int:
+        return self.H * self.dv
+
+    def side_weight(self):
+        return self.side_w
+
+    def out_weight(self):
+        return self.o_w
+
+    def inner(self, x, step, cache, sums=None, out=None, mult: float = 1.0):
+        """The o projection's input [T, n_heads * value_dim], times ``mult``, from ``sums``,
+        the 32-bit products of ``side_weight`` (q | f | v rows) with x."""
+        if cache is None or tuple(cache.spec.shape) != tuple(self.cache_spec().shape):
+            raise ValueError(f"forget-gate attention was given the cache "
+                             f"{None if cache is None else cache.spec}")
+        H, dk, dv = self.H, self.dk, self.dv
+        return ops.hgrn2_forward(sums, cache.state, self.f_bias, self.lower, self.norm_w, H=H, dk=dk,
+                                 dv=dv, q_col=0, f_col=H * dk, v_col=2 * H * dk,
+                                 norm_eps=self.norm_eps, cu_q=step.cu_q, slots=step.slots,
+                                 dtype=self.ctx.dtype, out_scale=mult, out=out)
+
+    def forward(self, x, step, cache):
+        y = self.inner(x, step, cache, self.proj(x, out_dtype=torch.float32))
+        return self.o(y, partial_ok=True)

@@ -5,7 +5,8 @@
 ``random_tensors`` yields the same tensors without a file, for models too large
 to be worth writing.  Every matrix and embedding is N(0, 0.02^2), every
 vector (norm weights) 1 + N(0, 0.1^2) and every offset (biases, vectors that are
-added to something) N(0, 0.1^2).  Each tensor has its own generator,
+added to something) N(0, 0.1^2); a fraction (a bound inside (0, 1)) is the sigmoid of
+N(0, 1), and the weights of an average are N(0, 0.1^2) with 1 added to the last.  Each tensor has its own generator,
 seeded from (seed, tensor name), so a tensor's values do not depend on which
 other tensors are made or in which order.
 
@@ -45,6 +46,11 @@ def random_tensor(name: str, spec: ParamSpec, seed: int, dtype=torch.bfloat16,
         x = 1.0 + VECTOR_STD * x
     elif spec.kind == "offset":
         x = VECTOR_STD * x
+    elif spec.kind == "fraction":
+        x = torch.sigmoid(x)
+    elif spec.kind == "average":
+        x = VECTOR_STD * x
+        x.reshape(-1)[-1] += 1.0
     else:
         x = MATRIX_STD * x
     return x.to(dtype)
