@@ -1,12 +1,12 @@
 from .base import (BuildContext, ParamSpec, Part, PartSpec, ProductChoice, build_part,
                    known_parts, register_part, unregister_part)
-from .block import Block, PostNormBlock, PreNormBlock, SandwichBlock
+from .block import Block, ParallelBlock, PostNormBlock, PreNormBlock, SandwichBlock
 from .feedforward import FeedForward, GatedMLP, ReluSquaredMLP, RoutedExperts, SwiGLU
 from .io import Embedding, Head, LinearHead, TokenEmbedding, TokenPositionalEmbedding
 from .linear import Linear
-from .mixer import GQAAttention, LatentAttention, Mixer
-from .recurrent import GatedDelta, GatedLinearRecurrence, Retention
-from .norm import Contribution, LayerNorm, Norm, RMSNorm, residual_add, stream_add
+from .mixer import GQAAttention, LatentAttention, Mixer, SideBySide
+from .recurrent import ForgetGateAttention, GatedDelta, GatedLinearRecurrence, Retention
+from .norm import Averaged, Contribution, LayerNorm, Norm, RMSNorm, residual_add, stream_add
 from .plan import LayerPlan, ModelPlan, ScheduleEntry
 from .position import NoPosition, PositionEncoding, RotaryHalfSplit, RotaryTable
 

@@ -291,6 +291,10 @@ class LayerNorm(Norm):
     def add_norm(self, res, delta, rows=None):
         post = None
         mult, offset = 1.0, None
+        if isinstance(delta, Averaged):          # resolved step by step, then normalised
+            res, delta, rows = delta.resolve(res, rows), None, None
+        elif isinstance(delta, (tuple, list)) or (isinstance(delta, Contribution) and delta.gate is not None):
+            res, delta = residual_add(res, resolve_terms(delta)), None
         if isinstance(delta, Contribution):
             c, delta = delta, delta.delta
             mult, offset = c.mult, c.offset

@@ -75,6 +75,14 @@ def visible(i, j, size, keep_first):
     return j <= i and ((size is None or i - j < size) or j < keep_first)
 
 
+def visibility(positions, size, keep_first):
+    """[T, T] bool: row i, column j is ``visible(positions[i], positions[j], ...)``."""
+    p = torch.as_tensor(positions, dtype=torch.long)
+    i, j = p[:, None], p[None, :]
+    near = torch.ones_like(i - j, dtype=torch.bool) if size is None else (i - j < size)
+    return (j <= i) & (near | (j < keep_first))
+
+
 def windowed_attention(h, positions, w, m, prefix=""):
     """The left mixer on h [T, width] with the tensors ``prefix + q/k/v/o/sink/g``."""
     T = h.shape[0]
@@ -88,8 +96,7 @@ def windowed_attention(h, positions, w, m, prefix=""):
         k = rotate_neighbours(k, positions, rot["base"], rot["dims"])
     mask = m.get("mask") or {}
     size, keep = mask.get("size"), int(mask.get("keep_first", 0))
-    see = torch.tensor([[visible(int(positions[i]), int(positions[j]), size, keep) for j in range(T)]
-                        for i in range(T)])
+    see = visibility(positions, size, keep)
     sink = w[prefix + "sink"].to(DT)
     gate = torch.sigmoid(h @ w[prefix + "g"].to(DT).T)                  # [T, H]
     out = torch.zeros(T, H, Dv, dtype=DT)
@@ -192,3 +199,20 @@ def forward(tokens, w, cfg, positions=None, streams=None):
             streams.append(x)
     h = norm_around_zero(x, w["final.norm"], cfg["norm"]["eps"])
     return h @ w["embed"].to(DT).T
+
+
+def logits(w, cfg, tokens, rows=None):
+    out = forward(tokens, w, cfg)
+    return out if rows is None else out[list(rows)]
+
+
+def greedy_generate(w, cfg, prompt, n_new, stop_ids=()):
+    """The first-maximum token after each step, the whole sequence run again every time."""
+    seq, new = list(prompt), []
+    for _ in range(n_new):
+        tok = int(torch.argmax(logits(w, cfg, seq, rows=[len(seq) - 1])[0]))
+        if tok in stop_ids:          # a stop token ends the request and is not part of its output
+            break
+        new.append(tok)
+        seq.append(tok)
+    return new
