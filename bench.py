@@ -21,7 +21,7 @@ weights, far more than the 126 MB L2, so nothing is flushed between timed steps.
                                        decode steps (launched one by one, an event pair
                                        around each): calls, time, GB/s, TFLOP/s, fractions
     python bench.py --requests S       the reference's request grid
-    python bench.py --designs [--design suvazen|sonalorn|zutazen] [--design-sizes 1b,4b,8b] [--batch B] [--design-ops]
+    python bench.py --designs [--design suvazen|sonalorn|zutazen|mananex] [--design-sizes 1b,4b,8b] [--batch B] [--design-ops]
                                        prefill and decode throughput of the Suvazen (or Sonalorn)
                                        design beside the Qwen3 decoder at equal layer sizes (random weights), and
                                        with --design-ops the per-kernel tables of both
@@ -227,6 +227,26 @@ def zutazen_config(size: str) -> dict:
                 layers=layers)
 
 
+def mananex_config(size: str) -> dict:
+    """The Mananex model of a size: the width, heads, head size, layers and vocabulary of
+    the Qwen3 model; every layer's mixer is attention (the Qwen3 model's heads, a quarter of
+    every head rotated, a window of 1,024 that keeps the first four tokens, sinks, a gate per
+    head) beside forget-gate linear attention (half as many heads, keys of half the head
+    size, values of the head size); every other layer has a dense feed-forward of the same
+    rows and the rest route three of eight experts of a quarter of the rows each; every
+    sublayer's result passes a residual gate of the stream's width, and the stream is the
+    depth average of all layers' results."""
+    W, nq, nkv, D, I, L, V = DESIGN_SIZES[size]
+    left = dict(heads=nq, kv_heads=nkv, dim=D, vdim=D, scale=D ** -0.5, rot={"base": 500000.0, "dims": D // 4},
+                mask={"size": 1024, "keep_first": 4})
+    right = dict(heads=nq // 2, dim=D // 2, vdim=D)
+    mixer = dict(left=left, right=right, left_scale=0.7, right_scale=1.1)
+    dense = {"kind": "dense", "ff": I}
+    moe = {"kind": "moe", "expert": {"ff": I // 4 // 64 * 64}, "router": {"experts": 8, "top": 3}}
+    layers = [dict(type="parallel", mixer=mixer, mlp=dense if i % 2 == 0 else moe) for i in range(L)]
+    return dict(architecture="Mananex", vocab=V, width=W, norm={"eps": 1e-6}, layers=layers)
+
+
 def design_configs(size: str, design: str = "suvazen"):
     W, nq, nkv, D, I, L, V = DESIGN_SIZES[size]
     qwen = dict(QWEN3_4B, hidden_size=W, num_attention_heads=nq, num_key_value_heads=nkv, head_dim=D,
@@ -242,6 +262,8 @@ def design_configs(size: str, design: str = "suvazen"):
         return {"qwen3": qwen, "sonalorn": sonalorn_config(size)}
     if design == "zutazen":       # beside the attention model and beside the other design with state and experts
         return {"qwen3": qwen, "sonalorn": sonalorn_config(size), "zutazen": zutazen_config(size)}
+    if design == "mananex":       # beside the attention model and beside the design with matrix states and experts
+        return {"qwen3": qwen, "zutazen": zutazen_config(size), "mananex": mananex_config(size)}
     return {"qwen3": qwen, "suvazen": suv}
 
 
@@ -302,10 +324,15 @@ def run_designs(sizes, batch: int, steps: int, warm: int, with_ops: bool, pk,
             torch.cuda.synchronize()
             dec_ms = a.elapsed_time(b) / steps
             n_weights = sum(t.numel() for t in _weights_of(eng))
-            kv_bytes = sum(st.k[:, :1].numel() * 2 * 2 // 64 for st in eng.cache.stores if hasattr(st, "k"))
+            stores = [x for st in eng.cache.stores for x in getattr(st, "stores", [st])]   # (a layer may have two needs)
+            kv_bytes = sum(st.k[:, :1].numel() * 2 * 2 // 64 for st in stores
+                           if hasattr(st, "k") and not st.spec.window)
+            # a window bounds the keys a step reads, whatever the sequence holds
+            win_bytes = sum(st.k[:, :1].numel() * 2 * 2 // 64 * (st.spec.window + st.spec.keep_first)
+                            for st in stores if hasattr(st, "k") and st.spec.window)
             # a recurrent mixer reads and writes its whole state every step
-            state_bytes = sum(2 * st.state[:, :1].numel() * 4 for st in eng.cache.stores if hasattr(st, "state"))
-            step_bytes = 2 * n_weights + batch * ((PROMPT + warm + steps / 2) * kv_bytes + state_bytes)
+            state_bytes = sum(2 * st.state[:, :1].numel() * 4 for st in stores if hasattr(st, "state"))
+            step_bytes = 2 * n_weights + batch * ((PROMPT + warm + steps / 2) * kv_bytes + win_bytes + state_bytes)
             out[size][design] = {
                 "prefill_ms": round(pre_ms, 3), "prefill_tok_s": round(PROMPT / pre_ms * 1e3, 1),
                 "decode_ms_per_step": round(dec_ms, 4), "decode_tok_s": round(batch / dec_ms * 1e3, 1),
@@ -472,8 +499,10 @@ def decode_timeline(eng, slots, V, g, pk, steps: int = 3) -> str:
     if n and len(labels) != len(ev) // n:
         print(f"bench.py: {len(labels)} launches were logged for a step of {len(ev) // n} kernels; "
               f"rows are named by kernel", file=sys.stderr)
-    kv = sum(eng.cache.length[s] for s in slots)
-    kv_spec = next((st.spec for st in eng.cache.stores if hasattr(st, "k")), None)
+    kv_spec = next((x.spec for st in eng.cache.stores for x in getattr(st, "stores", [st]) if hasattr(x, "k")), None)
+    # (a window, with the first tokens it keeps, bounds the keys a step reads)
+    reach = kv_spec.window + kv_spec.keep_first if kv_spec is not None and kv_spec.window else None
+    kv = sum(min(eng.cache.length[s], reach) if reach else eng.cache.length[s] for s in slots)
 
     def must_read(name):
         """Bytes a call of this kernel has to read: a product its weights, the decode
@@ -486,7 +515,7 @@ def decode_timeline(eng, slots, V, g, pk, steps: int = 3) -> str:
             return 2.0 * kv * 2 * kv_spec.n_kv_heads * kv_spec.head_dim
         return None
 
-    lines = [f"== decode step, batch {batch}, {kv // batch} keys a sequence, as it ran inside the captured "
+    lines = [f"== decode step, batch {batch}, {kv // batch} keys a sequence in reach, as it ran inside the captured "
              f"graph ({n} steps traced): {total / n:.1f} us a step; GB/s = what the kernel has to read / "
              f"its exposed time, of the {pk['source']} {pk['hbm_gbs']:.0f} GB/s",
              f"  {'kernel':<36}{'calls/step':>11}{'mean_us':>9}{'exposed_us':>11}{'per step':>10}{'share':>7}"
@@ -529,7 +558,7 @@ def main() -> int:
     ap.add_argument("--designs", action="store_true",
                     help="instead of the default run: the Suvazen design beside the Qwen3 decoder at "
                          "equal layer sizes (--design-sizes), prefill and decode at --batch")
-    ap.add_argument("--design", default="suvazen", choices=["suvazen", "sonalorn", "zutazen"],
+    ap.add_argument("--design", default="suvazen", choices=["suvazen", "sonalorn", "zutazen", "mananex"],
                     help="which design --designs sets beside Qwen3")
     ap.add_argument("--design-sizes", default="1b,4b,8b",
                     help=f"which of {sorted(DESIGN_SIZES)} --designs runs")

@@ -286,12 +286,43 @@ __global__ void head_gate_kernel(const T* __restrict__ x, const float* __restric
   pdl_launch_dependents_if_large();
   out[t * out_ld + i] = from_f32<T>(to_f32<T>(x[(t * nq + h) * Ds + d]) * g * mult);
 }
+// The same in 16-byte pieces (a thread takes 16 / sizeof(T) neighbours of one head), two rows a
+// block where a row has few pieces.
+template <typename T>
+__global__ void __launch_bounds__(256) head_gate_vec_kernel(const T* __restrict__ x, const float* __restrict__ gate,
+                                                            long long gate_ld, T* __restrict__ out, long long out_ld,
+                                                            int n_rows, int nq, int Ds, int Dv, float mult) {
+  constexpr int V = 16 / (int)sizeof(T);
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  const int per_row = nq * Dv / V;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)n_rows * per_row) return;
+  const size_t t = (size_t)(i / per_row);
+  const int p = (int)(i % per_row), h = p / (Dv / V), d = (p % (Dv / V)) * V;
+  const float g = (gate ? 1.0f / (1.0f + expf(-gate[t * gate_ld + h])) : 1.0f) * mult;
+  const uint4 raw = *reinterpret_cast<const uint4*>(x + (t * nq + h) * Ds + d);
+  const T* v = reinterpret_cast<const T*>(&raw);
+  uint4 res;
+  T* o = reinterpret_cast<T*>(&res);
+#pragma unroll
+  for (int e = 0; e < V; ++e) o[e] = from_f32<T>(to_f32<T>(v[e]) * g);
+  pdl_launch_dependents_if_large();
+  *reinterpret_cast<uint4*>(out + t * out_ld + (size_t)h * Dv + d) = res;
+}
 template <typename T>
 static int head_gate(const void* x, const float* gate, long long gate_ld, void* out, long long out_ld,
                      int n_rows, int nq, int Ds, int Dv, float mult, cudaStream_t s) {
   if (n_rows < 0 || nq <= 0 || Dv <= 0 || Ds < Dv || !x || !out || out_ld < (long long)nq * Dv ||
       (gate && gate_ld < nq))
     return GB_ERR_BAD_ARG;
+  if (n_rows == 0) return 0;
+  constexpr int V = 16 / (int)sizeof(T);
+  if (Dv % V == 0 && Ds % V == 0 && out_ld % V == 0 && ((((uintptr_t)x) | ((uintptr_t)out)) & 15) == 0) {
+    const long long pieces = (long long)n_rows * (nq * Dv / V);
+    return gb_launch(head_gate_vec_kernel<T>, dim3((unsigned)((pieces + 255) / 256)), dim3(256), 0, s,
+                     (const T*)x, gate, gate_ld, (T*)out, out_ld, n_rows, nq, Ds, Dv, mult);
+  }
   for (int r0 = 0; r0 < n_rows; r0 += 65535) {      // rows go to grid.y
     const int n = n_rows - r0 < 65535 ? n_rows - r0 : 65535;
     int e = gb_launch(head_gate_kernel<T>, dim3((nq * Dv + 255) / 256, n), dim3(256), 0, s,

@@ -118,7 +118,7 @@ class Model:
             history = torch.empty((len(self.plan.schedule) + 1, step.n_tokens, self.embedding.hidden),
                                   dtype=torch.float32, device=step.tokens.device)
             self.embedding.forward(step.tokens, step, out=history[0])
-            pending = self.embedding.forward(step.tokens, step)
+            pending = history[0].clone()
         else:
             pending = self.embedding.forward(step.tokens, step)
         res = None

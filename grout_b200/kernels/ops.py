@@ -248,9 +248,10 @@ def embed(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
 
 @_profiled("embed_scaled", lambda out, table, ids, scale, **k: (_nbytes(ids, out) + out.numel() * table.element_size(), 0))
 def embed_scaled(table: torch.Tensor, ids: torch.Tensor, scale: float,
-                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 into: Optional[torch.Tensor] = None) -> torch.Tensor:
     """scale * table[ids[t]] as 32-bit rows [T, H] (the product is 32-bit whatever the table's
-    type), written into ``out`` when given."""
+    type), written into ``into`` when given."""
+    out = into
     _need(table, "embedding table", ndim=2)
     _need(ids, "token ids", torch.int32, 1)
     V, H = table.shape
@@ -1870,7 +1871,12 @@ class _Hgrn2Args(ctypes.Structure):
     _fields_ = [("proj", _P), ("ld", _L), ("q_col", _I), ("f_col", _I), ("v_col", _I), ("f_bias", _P),
                 ("lower", _P), ("norm_w", _P), ("cu_q", _P), ("slots", _P), ("state", _P),
                 ("state_stride", _L), ("o", _P), ("y", _P), ("y_ld", _L), ("n_tokens", _I),
-                ("n_seqs", _I), ("H", _I), ("dk", _I), ("dv", _I), ("norm_eps", _F), ("out_scale", _F)]
+                ("n_seqs", _I), ("H", _I), ("dk", _I), ("dv", _I), ("norm_eps", _F), ("out_scale", _F),
+                ("qb", _P), ("chunk_state", _P), ("chunk_decay", _P), ("max_rows", _I)]
+
+
+HGRN2_CHUNK = 64          # rows of a chunk of the kernel's chunked form (HG_CHUNK)
+HGRN2_CHUNK_MIN = 256     # a sequence of this many rows in a step: the step goes chunk by chunk
 
 
 def _cost_hgrn2(out, proj, state, *a, H, dk, dv, **k):
@@ -1887,14 +1893,18 @@ def _cost_hgrn2(out, proj, state, *a, H, dk, dv, **k):
 def hgrn2_forward(proj: torch.Tensor, state: torch.Tensor, f_bias: torch.Tensor, lower: torch.Tensor,
                   norm_w: torch.Tensor, *, H: int, dk: int, dv: int, q_col: int, f_col: int,
                   v_col: int, norm_eps: float, cu_q, slots, dtype: torch.dtype,
-                  out_scale: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                  out_scale: float = 1.0, into: Optional[torch.Tensor] = None,
+                  max_rows: int = 0) -> torch.Tensor:
     """Linear attention whose forget gate decides what is written, on the 32-bit sums of a
     projection ``proj`` [T, ld] whose columns from ``q_col``, ``f_col`` (H dk each) and
     ``v_col`` (H dv) are this mixer's: q = silu(zq), f = lower + (1 - lower) sigmoid(zf +
     f_bias); per head S <- diag(f) S + (1 - f) v^T, o = S^T q; y = rmsnorm(o) * norm_w *
     out_scale in ``dtype``.  ``state`` [slots + 1, H dk dv] (32-bit) is read and updated for
-    the sequences of ``cu_q`` whose slot is not negative.  ``out``: a 2-D view [T, H dv] of a
-    wider row to write into (its row pitch is kept); else a new tensor."""
+    the sequences of ``cu_q`` whose slot is not negative.  ``into``: a 2-D view [T, H dv] of a
+    wider row to write into (its row pitch is kept); else a new tensor.  ``max_rows``: the most
+    rows a sequence brings (0: unknown, taken as all of them); from ``HGRN2_CHUNK_MIN`` on the step
+    goes chunk by chunk (the same sums in another order)."""
+    out = into
     if (proj is None or not proj.is_cuda or proj.dtype != torch.float32 or proj.dim() != 2
             or proj.stride(1) != 1):
         raise KernelError("projection sums must be a 32-bit [T, columns] CUDA view with unit stride")
@@ -1924,8 +1934,16 @@ def hgrn2_forward(proj: torch.Tensor, state: torch.Tensor, f_bias: torch.Tensor,
     a.o, a.y, a.y_ld = o.data_ptr(), out.data_ptr(), out.stride(0)
     a.n_tokens, a.n_seqs, a.H, a.dk, a.dv = T, slots.shape[0], int(H), int(dk), int(dv)
     a.norm_eps, a.out_scale = float(norm_eps), float(out_scale)
+    a.max_rows = int(max_rows) if max_rows else T
+    chunked = a.max_rows >= HGRN2_CHUNK_MIN
+    if chunked:
+        entries = T // HGRN2_CHUNK + slots.shape[0]
+        qb = torch.empty((T, H, dk), dtype=torch.float32, device=proj.device)
+        chunk_state = torch.empty((entries, H, dk, dv), dtype=torch.float32, device=proj.device)
+        chunk_decay = torch.empty((entries, H, dk), dtype=torch.float32, device=proj.device)
+        a.qb, a.chunk_state, a.chunk_decay = qb.data_ptr(), chunk_state.data_ptr(), chunk_decay.data_ptr()
     _check(_fn("hgrn2", f"gb_hgrn2_{_suffix(dtype)}", "pp")(ctypes.addressof(a), _stream()),
-           "hgrn2_forward", 2)
+           "hgrn2_forward", 4 if chunked else 2)
     return out
 
 
@@ -2013,11 +2031,12 @@ def gated_norm(res_in: Optional[torch.Tensor], terms, *, dtype: torch.dtype,
 
 @_profiled("head_gate", lambda out, x, gate, *a, **k: (_nbytes(x) + out.numel() * out.element_size(), 0))
 def head_gate(x: torch.Tensor, gate: Optional[torch.Tensor], v_dim: int, mult: float = 1.0,
-              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+              into: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[t, h * v_dim + d] = x[t, h, d] * sigmoid(gate[t, h]) * mult for d < v_dim, with x
     [T, heads, Ds] (Ds >= v_dim), ``gate`` a 32-bit 2-D view [T, heads] of logits whose row
-    pitch is kept (None: no gate), and ``out`` a 2-D view [T, heads * v_dim] of a wider row
+    pitch is kept (None: no gate), and ``into`` a 2-D view [T, heads * v_dim] of a wider row
     to write into, or None for a new tensor."""
+    out = into
     _need(x, "heads", ndim=3)
     T, nq, Ds = x.shape
     if gate is not None and (gate.dtype != torch.float32 or tuple(gate.shape) != (T, nq) or gate.stride(1) != 1

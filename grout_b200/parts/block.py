@@ -188,7 +188,8 @@ class ParallelBlock(Block):
     sublayer's result is multiplied element by element by sigmoid(W h + b) ("gated
     residual"), W and b being the tensors ``gate1`` / ``gate2`` (local names; the bias is
     the name + ``bias_suffix``) under the layer's prefix; both gates' logits come from one
-    product with 32-bit sums.  The sublayers' results leave as a tuple of
+    product with 32-bit sums, which also takes the rows that the mixer wants multiplied with h in
+    32-bit, if it has some to lend (``lend_side_weight``).  The sublayers' results leave as a tuple of
     ``Contribution``s, so the sum into the stream is done by the kernel of whoever reads
     the stream next (the next layer's norm, or the model's last one)."""
 
@@ -205,6 +206,7 @@ class ParallelBlock(Block):
         self.width = self.norm1.dim
         self.gates = None
         self.gate_bias = (None, None)
+        self.n_gate_cols, self.mixer_sums = 0, False
 
     def named_parts(self) -> Dict[str, Part]:
         roles = ("norm1", "mixer", "feedforward")
@@ -227,6 +229,15 @@ class ParallelBlock(Block):
         ws = [params[n] for n in names]
         if len({w.dtype for w in ws}) > 1:
             raise ValueError("the two residual gates must be stored in one dtype to be fused")
+        # a mixer that needs 32-bit products with h of its own (``SideBySide``) hands its rows over:
+        # one product then serves the gates and the mixer
+        self.n_gate_cols = sum(w.shape[0] for w in ws)
+        side = self.mixer.lend_side_weight() if hasattr(self.mixer, "lend_side_weight") else None
+        if side is not None and side.dtype == ws[0].dtype:
+            ws = ws + [side]
+        elif side is not None:
+            self.mixer.keep_side_weight(side)
+        self.mixer_sums = side is not None and len(ws) > len(names)
         self.gates = Linear(torch.cat(ws, dim=0) if len(ws) > 1 else ws[0], self.ctx.products)
         # 32-bit whatever the checkpoint stores: the sum into the stream is 32-bit
         self.gate_bias = tuple(params[n + self.bias_suffix].float().contiguous() if n else None
@@ -246,7 +257,10 @@ class ParallelBlock(Block):
         res, h = self.norm1.add_norm(res, pending)
         W = self.width
         logits = self.gates(h, out_dtype=torch.float32) if self.gated else None
-        a = self.mixer.forward(h, step, cache)
+        if self.gated and self.mixer_sums:
+            a = self.mixer.forward(h, step, cache, sums=logits[:, self.n_gate_cols:])
+        else:
+            a = self.mixer.forward(h, step, cache)
         terms = [Contribution(a, gate=logits[:, :W] if self.gated else None, gate_bias=self.gate_bias[0])]
         if self.feedforward is not None:
             m = self.feedforward.forward(h, step)

@@ -48,7 +48,7 @@ class TokenEmbedding(Embedding):
 
     def forward(self, tokens, step, out=None):
         if self.scale is not None:
-            return ops.embed_scaled(self.weight, tokens, self.scale, out=out)
+            return ops.embed_scaled(self.weight, tokens, self.scale, into=out)
         x = ops.embed(self.weight, tokens)
         return ops.cast(x, self.ctx.dtype) if x.dtype != self.ctx.dtype else x
 

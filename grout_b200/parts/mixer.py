@@ -211,7 +211,7 @@ class GQAAttention(Mixer):
         outputs under their gates (``sums``: the 32-bit products of ``side_weight`` with
         x), written into ``out`` when given."""
         attn = self._attend(x, step, cache)
-        return ops.head_gate(attn, sums if self.head_gate else None, self.Dv, mult, out)
+        return ops.head_gate(attn, sums if self.head_gate else None, self.Dv, mult, into=out)
 
     def captures_prompts(self):
         # an encoding with arithmetic of its own runs between two kernels here and
@@ -337,17 +337,30 @@ class SideBySide(Mixer):
         mods = self.o.kernel_modules() if self.o else ()
         return mods + (self.side.kernel_modules() if self.side else ())
 
+    def lend_side_weight(self):
+        """The rows of the side product, for a block that multiplies h by rows of its own in
+        32-bit anyway and takes these along (it then passes ``sums`` to ``forward``); None when
+        there are none.  The mixer's own product is given up."""
+        if self.side is None:
+            return None
+        w, self.side = self.side.weight, None
+        return w
+
+    def keep_side_weight(self, w) -> None:
+        self.side = Linear(w, self.ctx.products)
+
     def cache_spec(self):
         return SideBySideSpec(tuple(p.cache_spec() for p in self.parts))
 
     def captures_prompts(self):
         return True
 
-    def forward(self, x, step, cache):
+    def forward(self, x, step, cache, sums=None):
         if not isinstance(cache, tuple) or len(cache) != len(self.parts):
             raise ValueError(f"{len(self.parts)} mixers side by side were given the cache {cache!r}")
         T = x.shape[0]
-        sums = self.side(x, out_dtype=torch.float32) if self.side is not None else None
+        if sums is None and self.side is not None:
+            sums = self.side(x, out_dtype=torch.float32)
         wide = torch.empty((T, self.o.in_features), dtype=self.ctx.dtype, device=x.device)
         for p, view, scale, (s0, sn), (i0, n) in zip(self.parts, cache, self.scales, self.side_cols,
                                                      self.inner_cols):

@@ -348,7 +348,7 @@ class ForgetGateAttention(Mixer):
         return ops.hgrn2_forward(sums, cache.state, self.f_bias, self.lower, self.norm_w, H=H, dk=dk,
                                  dv=dv, q_col=0, f_col=H * dk, v_col=2 * H * dk,
                                  norm_eps=self.norm_eps, cu_q=step.cu_q, slots=step.slots,
-                                 dtype=self.ctx.dtype, out_scale=mult, out=out)
+                                 dtype=self.ctx.dtype, out_scale=mult, into=out, max_rows=step.max_q_len)
 
     def forward(self, x, step, cache):
         y = self.inner(x, step, cache, self.proj(x, out_dtype=torch.float32))

@@ -114,6 +114,38 @@ def test_forget_gate_attention_whole_in_portions_and_token_by_token(m):
     close(scaled, 0.7 * want, torch.float32, "a factor, and sums that are part of a wider row")
 
 
+@pytest.mark.parametrize("m", [dict(heads=2, dim=64, vdim=48), dict(heads=3, dim=20, vdim=130),
+                               dict(heads=1, dim=100, vdim=24)])
+def test_forget_gate_attention_long_sequences_go_chunk_by_chunk(m):
+    """A sequence that brings 256 rows or more in a step goes chunk by chunk: the same sums in another
+    order.  Lengths at the chunks' edges; a state that is there already; another sequence of a few rows,
+    a padding sequence and one more long sequence in the same step; gates that forget at once and gates
+    that keep nearly everything side by side."""
+    from grout_b200.kernels import ops
+    H, dk, dv, W = m["heads"], m["dim"], m["vdim"], 24
+    w = _fg_weights(m, W, seed=61, f_scale=4.0)
+    wp = torch.cat([w[k] for k in ("q", "f", "v")], 0).double()
+    for T in (256, 257, 320, 383, 1000):
+        xs = rnd(40 + T, W, seed=62)
+        want, S_want = _fg_plain(w, m, xs)
+        got, state = _fg_run(w, m, xs, [40, T], torch.float32)      # 40 rows row by row first, then the long step
+        close(got, want, torch.float32, f"{T} rows after 40")
+        close(state[0].view(H, dk, dv), S_want, torch.float32, "state")
+    a, b, c = rnd(300, W, seed=63), rnd(5, W, seed=64), rnd(450, W, seed=65)
+    pad = rnd(70, W, seed=66)
+    state = torch.zeros(5, H * dk * dv, device=DEV)
+    rows = torch.cat([a, b, pad, c])
+    step = make_step([(1, 0, 300), (3, 0, 5), (-1, 0, 70), (0, 0, 450)])
+    y = ops.hgrn2_forward(g32(rows.double() @ wp.T), state, g32(w["f.b"]), g32(w["lower"]), g32(w["norm"]),
+                          H=H, dk=dk, dv=dv, q_col=0, f_col=H * dk, v_col=2 * H * dk, norm_eps=1e-5,
+                          cu_q=step.cu_q, slots=step.slots, dtype=torch.float32, max_rows=step.max_q_len).cpu()
+    for xs, (lo, hi), slot in ((a, (0, 300), 1), (b, (300, 305), 3), (c, (375, 825), 0)):
+        want, S_want = _fg_plain(w, m, xs)
+        close(y[lo:hi], want, torch.float32, f"rows {lo}..{hi}")
+        close(state[slot].view(H, dk, dv).cpu(), S_want, torch.float32, f"state of slot {slot}")
+    assert float(state[2].abs().max()) == 0.0 and float(state[4].abs().max()) == 0.0
+
+
 def test_forget_gate_attention_batches_slots_used_again_and_padding():
     """Three sequences of unequal length in one step with a padding sequence between them; then a
     slot is zeroed and used by another sequence, which must not see what was there."""
@@ -173,8 +205,9 @@ def test_forget_gate_attention_reads_a_far_value():
     assert float(S[0, 0].abs().max()) > 1e-3 and float(S[0, 1].abs().max()) < 1e-12
     whole, state = _fg_run(w, m, xs, [T], torch.float32)
     close(state[0].view(1, 2, 4), S, torch.float32, "state after 400 tokens")
-    steps, state1 = _fg_run(w, m, xs, [1] * T, torch.float32)
-    assert torch.equal(state1[0], state[0]) and torch.equal(steps, whole)
+    steps, state1 = _fg_run(w, m, xs, [1] * T, torch.float32)     # (the whole went chunk by chunk)
+    close(state1[0].view(1, 2, 4), S, torch.float32, "state, token by token")
+    close(steps, want, torch.float32, "read-outs, token by token")
     close(whole, want, torch.float32, "read-outs")
 
 
@@ -331,16 +364,17 @@ def test_a_planted_key_at_every_edge(dtype, D):
 
 # ------------------------------------------------------------------ small pieces
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_gate_per_head_drops_the_filling_and_writes_into_a_wider_row(dtype):
+@pytest.mark.parametrize("sizes", [(37, 3, 32, 20, 7, 5), (70, 4, 64, 48, 16, 8), (5, 2, 128, 128, 0, 0)])
+def test_gate_per_head_drops_the_filling_and_writes_into_a_wider_row(dtype, sizes):
     from grout_b200.kernels import ops
-    T, H, Ds, Dv = 37, 3, 32, 20
+    T, H, Ds, Dv, before, after = sizes         # (odd sizes take single values, the others 16-byte pieces)
     x = rnd(T, H, Ds, seed=1).to(dtype)
     logits = rnd(T, H + 2, seed=2, scale=2.0)
-    wide = torch.full((T, 7 + H * Dv + 5), 9.0, dtype=dtype, device=DEV)
-    out = ops.head_gate(x.to(DEV), logits.to(DEV)[:, 1:1 + H], Dv, 0.8, out=wide[:, 7:7 + H * Dv])
+    wide = torch.full((T, before + H * Dv + after), 9.0, dtype=dtype, device=DEV)
+    out = ops.head_gate(x.to(DEV), logits.to(DEV)[:, 1:1 + H], Dv, 0.8, into=wide[:, before:before + H * Dv])
     want = x.double()[:, :, :Dv] * torch.sigmoid(logits.double()[:, 1:1 + H])[:, :, None] * 0.8
     close(out.float().cpu(), want.reshape(T, H * Dv), dtype)
-    assert bool((wide[:, :7] == 9.0).all()) and bool((wide[:, 7 + H * Dv:] == 9.0).all())
+    assert bool((wide[:, :before] == 9.0).all()) and bool((wide[:, before + H * Dv:] == 9.0).all())
     plain_out = ops.head_gate(x.to(DEV), None, Dv)
     close(plain_out.float().cpu(), x.double()[:, :, :Dv].reshape(T, H * Dv), dtype)
 
@@ -373,34 +407,35 @@ def test_rotation_of_neighbouring_pairs_in_the_qk_kernel(dtype, shape):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_gated_sums_depth_average_and_norm_in_one_kernel(dtype):
+@pytest.mark.parametrize("sizes", [(19, 100, 2), (8, 1024, 0), (100, 1024, 4), (3, 4096, 0)])
+def test_gated_sums_depth_average_and_norm_in_one_kernel(dtype, sizes):
     """X = x + sigmoid(g1 + b1) d1 + sigmoid(g2 + b2) d2 is stored among the earlier results, the
     stream becomes their weighted sum and is normalised; terms as activations and as stacks of
     partial sums, one term, no gate, no average, a row list."""
     from grout_b200.kernels import ops
-    T, N, n_hist = 19, 100, 3
-    x = rnd(T, N, seed=1)
+    (T, N, g0), n_hist = sizes, 11       # (rows that are no multiple of four take single loads; few rows of a
+    x = rnd(T, N, seed=1)                #  wide stream a cluster of blocks each; more than eight earlier results)
     d1, d2 = rnd(T, N, seed=2).to(dtype), rnd(3, T, N, seed=3)
-    gates = rnd(T, 2 * N + 4, seed=4, scale=2.0)
+    gates = rnd(T, 2 * N + 8, seed=4, scale=2.0)
     b1, b2 = rnd(N, seed=5), rnd(N, seed=6)
     hist = rnd(n_hist + 2, T, N, seed=7)
     aw, nw = rnd(n_hist + 1, seed=8), 1 + rnd(N, seed=9, scale=0.2)
-    X = (x.double() + torch.sigmoid(gates.double()[:, 2:2 + N] + b1.double()) * d1.double()
-         + torch.sigmoid(gates.double()[:, 2 + N:2 + 2 * N] + b2.double()) * d2.double().sum(0))
+    X = (x.double() + torch.sigmoid(gates.double()[:, g0:g0 + N] + b1.double()) * d1.double()
+         + torch.sigmoid(gates.double()[:, g0 + N:g0 + 2 * N] + b2.double()) * d2.double().sum(0))
     avg = plain.depth_average(list(hist[:n_hist].double()) + [X], aw)
     y_want = plain.rms(avg, 1e-5) * nw.double()
     hd, gd = hist.to(DEV).clone(), gates.to(DEV)
-    res, y = ops.gated_norm(x.to(DEV).clone(), [(d1.to(DEV), gd[:, 2:2 + N], b1.to(DEV)),
-                                                (d2.to(DEV), gd[:, 2 + N:2 + 2 * N], b2.to(DEV))],
+    res, y = ops.gated_norm(x.to(DEV).clone(), [(d1.to(DEV), gd[:, g0:g0 + N], b1.to(DEV)),
+                                                (d2.to(DEV), gd[:, g0 + N:g0 + 2 * N], b2.to(DEV))],
                             dtype=dtype, hist=hd, n_hist=n_hist, avg_w=aw.to(DEV), norm_w=nw.to(DEV), eps=1e-5)
     close(hd[n_hist].cpu(), X, torch.float32, "the layer's result among the earlier ones")
     assert torch.equal(hd[n_hist + 1].cpu(), hist[n_hist + 1])
     close(res.cpu(), avg, torch.float32, "the stream")
     close(y.float().cpu(), y_want, dtype, "normalised")
-    rows = torch.tensor([4, 0, 18], dtype=torch.int32)
+    rows = torch.tensor([2, 0, T - 1], dtype=torch.int32)
     hd2 = hist.to(DEV).clone()
-    res2, y2 = ops.gated_norm(x.to(DEV), [(d1.to(DEV), gd[:, 2:2 + N], b1.to(DEV)),
-                                          (d2.to(DEV), gd[:, 2 + N:2 + 2 * N], b2.to(DEV))],
+    res2, y2 = ops.gated_norm(x.to(DEV), [(d1.to(DEV), gd[:, g0:g0 + N], b1.to(DEV)),
+                                          (d2.to(DEV), gd[:, g0 + N:g0 + 2 * N], b2.to(DEV))],
                               dtype=dtype, hist=hd2, n_hist=n_hist, avg_w=aw.to(DEV), rows=rows.to(DEV),
                               norm_w=nw.to(DEV), eps=1e-5)
     close(res2.cpu(), avg[rows.long()], torch.float32, "picked rows")
