@@ -81,9 +81,23 @@ template <int V> __device__ __forceinline__ void gn_store(bf16* p, const float (
 // The new stream's V values at columns n .. n + V - 1 of source row t; the layer's result is
 // stored among the earlier ones on the way.  Loads that do not depend on one another (the
 // partial sums, the earlier results) are requested together and used in order.
-template <typename T, int V>
+// GN_AHEAD: how many earlier results are requested at a time: many where a step has few rows (the
+// time is the loads' round trips), fewer where it has many (registers decide how many rows an SM holds)
+template <typename T, int V, int GN_AHEAD>
 __device__ __forceinline__ void gn_values(const GatedNormArgs& a, size_t t, int n, float (&xp)[V]) {
   const int N = a.N;
+  // the first earlier results depend on nothing of this layer: they are requested first and
+  // are on their way while the layer's own terms are put together
+  constexpr bool EARLY = GN_AHEAD > 8;
+  constexpr int PARTS = EARLY ? 8 : 4;      // partial sums requested at a time
+  float hv[GN_AHEAD][V];
+  if (EARLY && a.hist) {
+#pragma unroll
+    for (int u = 0; u < GN_AHEAD; ++u) {
+      const int j = u < a.n_hist ? u : (a.n_hist > 0 ? a.n_hist - 1 : 0);
+      if (a.n_hist > 0) gn_load<V>(a.hist + (size_t)j * a.hist_stride + t * N + n, hv[u]);
+    }
+  }
   float X[V];
 #pragma unroll
   for (int e = 0; e < V; ++e) X[e] = 0.f;
@@ -92,21 +106,23 @@ __device__ __forceinline__ void gn_values(const GatedNormArgs& a, size_t t, int 
   for (int c = 0; c < 2; ++c) {
     const GatedTerm& g = a.term[c];
     if (!g.delta && !g.parts) continue;
-    float d[V];
+    float d[V], z[V], b[V];
 #pragma unroll
-    for (int e = 0; e < V; ++e) d[e] = 0.f;
+    for (int e = 0; e < V; ++e) d[e] = 0.f, z[e] = 0.f, b[e] = 0.f;
+    if (g.gate) gn_load<V>(g.gate + t * g.gate_ld + n, z);
+    if (g.gate && g.gate_bias) gn_load<V>(g.gate_bias + n, b);
     if (g.delta) {
       gn_load<V>((const T*)g.delta + t * N + n, d);
     } else {
-      for (int k0 = 0; k0 < g.n_parts; k0 += 4) {
-        float pk[4][V];
+      for (int k0 = 0; k0 < g.n_parts; k0 += PARTS) {
+        float pk[PARTS][V];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < PARTS; ++u) {
           const int k = k0 + u < g.n_parts ? k0 + u : g.n_parts - 1;
           gn_load<V>(g.parts + (size_t)k * g.part_stride + t * N + n, pk[u]);
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
+        for (int u = 0; u < PARTS; ++u)
           if (k0 + u < g.n_parts) {
 #pragma unroll
             for (int e = 0; e < V; ++e) d[e] += pk[u][e];
@@ -114,11 +130,6 @@ __device__ __forceinline__ void gn_values(const GatedNormArgs& a, size_t t, int 
       }
     }
     if (g.gate) {
-      float z[V], b[V];
-      gn_load<V>(g.gate + t * g.gate_ld + n, z);
-#pragma unroll
-      for (int e = 0; e < V; ++e) b[e] = 0.f;
-      if (g.gate_bias) gn_load<V>(g.gate_bias + n, b);
 #pragma unroll
       for (int e = 0; e < V; ++e) d[e] *= gn_sigmoid(z[e] + b[e]);
     }
@@ -133,15 +144,16 @@ __device__ __forceinline__ void gn_values(const GatedNormArgs& a, size_t t, int 
   if (!a.rows) gn_store<V>(a.hist + (size_t)a.n_hist * a.hist_stride + t * N + n, X);
 #pragma unroll
   for (int e = 0; e < V; ++e) xp[e] = 0.f;
-  for (int j0 = 0; j0 < a.n_hist; j0 += 8) {
-    float hv[8][V];
+  for (int j0 = 0; j0 < a.n_hist; j0 += GN_AHEAD) {
+    if (j0 > 0 || !EARLY) {
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const int j = j0 + u < a.n_hist ? j0 + u : a.n_hist - 1;
-      gn_load<V>(a.hist + (size_t)j * a.hist_stride + t * N + n, hv[u]);
+      for (int u = 0; u < GN_AHEAD; ++u) {
+        const int j = j0 + u < a.n_hist ? j0 + u : a.n_hist - 1;
+        gn_load<V>(a.hist + (size_t)j * a.hist_stride + t * N + n, hv[u]);
+      }
     }
 #pragma unroll
-    for (int u = 0; u < 8; ++u)
+    for (int u = 0; u < GN_AHEAD; ++u)
       if (j0 + u < a.n_hist) {
         const float w = a.avg_w[j0 + u];
 #pragma unroll
@@ -164,7 +176,7 @@ __global__ void __launch_bounds__(256) gated_norm_kernel(const GatedNormArgs a) 
   float ss = 0.f;
   for (int n = threadIdx.x * V; n < N; n += blockDim.x * V) {
     float xp[V];
-    gn_values<T, V>(a, t, n, xp);
+    gn_values<T, V, 8>(a, t, n, xp);
     gn_store<V>(gn_row + n, xp);
 #pragma unroll
     for (int e = 0; e < V; ++e) ss = fmaf(xp[e], xp[e], ss);
@@ -209,7 +221,7 @@ __global__ void gated_norm_cluster_kernel(const GatedNormArgs a) {
   float xp[4] = {0.f, 0.f, 0.f, 0.f};
   float ss = 0.f;
   if (active) {
-    gn_values<T, 4>(a, t, n, xp);
+    gn_values<T, 4, 16>(a, t, n, xp);
 #pragma unroll
     for (int e = 0; e < 4; ++e) ss = fmaf(xp[e], xp[e], ss);
     if (a.res_out) gn_store<4>(a.res_out + (size_t)r * N + n, xp);

@@ -77,63 +77,44 @@ __device__ __forceinline__ int hg_row(int lane, int r) {
   return (KPL % 4 == 0) ? (r >> 2) * 32 + lane * 4 + (r & 3) : r * HG_LANES + lane;
 }
 
-// CHUNKED: the block owns one chunk of its sequence, starts from zeros and leaves what the
-// chunk adds to the state in the chunk's entry instead of the sequence's state.
-template <int KPL, bool CHUNKED>
+// CPT: columns of S a thread owns (the rows' q and f are read from shared memory once for all
+// of them).  CHUNKED: the block owns one chunk of its sequence, starts from zeros and leaves
+// what the chunk adds to the state in the chunk's entry instead of the sequence's state.
+template <int KPL, int CPT, bool CHUNKED>
 __global__ void __launch_bounds__(HG_COLS* HG_LANES) hgrn2_scan_kernel(const Hgrn2Args a) {
   constexpr int DKP = KPL * HG_LANES;            // dk rounded up; the rest is q = 0, f = 1
+  constexpr int BC = HG_COLS * CPT;              // columns a block owns
   __shared__ __align__(16) float qs[HG_STAGE][DKP];
   __shared__ __align__(16) float fs[HG_STAGE][DKP];
-  __shared__ float vs[HG_STAGE][HG_COLS];
+  __shared__ float vs[HG_STAGE][BC];
   __shared__ float bs[CHUNKED ? DKP : 1];        // the product of the chunk's gates so far
   pdl_launch_dependents_if_small();
   pdl_wait();
-  const int col_tiles = (a.dv + HG_COLS - 1) / HG_COLS;
-  const int h = blockIdx.x, seq = blockIdx.y, c0 = (blockIdx.z % col_tiles) * HG_COLS;
+  const int col_tiles = (a.dv + BC - 1) / BC;
+  const int h = blockIdx.x, seq = blockIdx.y, c0 = (blockIdx.z % col_tiles) * BC;
   const int z = blockIdx.z / col_tiles;          // the chunk (0 unless CHUNKED)
   const int dk = a.dk, dv = a.dv;
   const int seq_first = a.cu_q[seq], seq_n = a.cu_q[seq + 1] - seq_first;
   const int first = seq_first + z * HG_CHUNK;
   const int n = CHUNKED ? min(HG_CHUNK, seq_n - z * HG_CHUNK) : seq_n;
   if (n <= 0) return;
-  const int tid = threadIdx.x, lane = tid % HG_LANES, col = c0 + tid / HG_LANES;
-  const bool live = col < dv;
+  const int tid = threadIdx.x, lane = tid % HG_LANES, cb = c0 + (tid / HG_LANES) * CPT;
   const int slot = a.slots[seq];
   float* sp = CHUNKED ? a.chunk_state + (hg_entry(seq_first, z, seq) * a.H + h) * (size_t)dk * dv
                       : (slot >= 0 ? a.state + (size_t)slot * a.state_stride + (size_t)h * dk * dv : nullptr);
-  float S[KPL];
+  float S[CPT][KPL];
 #pragma unroll
-  for (int r = 0; r < KPL; ++r) {
-    const int i = hg_row<KPL>(lane, r);
-    S[r] = (!CHUNKED && sp && live && i < dk) ? sp[(size_t)i * dv + col] : 0.f;
-  }
+  for (int c = 0; c < CPT; ++c)
+#pragma unroll
+    for (int r = 0; r < KPL; ++r) {
+      const int i = hg_row<KPL>(lane, r);
+      S[c][r] = (!CHUNKED && sp && cb + c < dv && i < dk) ? sp[(size_t)i * dv + cb + c] : 0.f;
+    }
   if (CHUNKED)
     for (int e = tid; e < DKP; e += blockDim.x) bs[e] = 1.f;
   for (int t0 = 0; t0 < n; t0 += HG_STAGE) {
     const int nt = min(HG_STAGE, n - t0);
     __syncthreads();
-    if (CHUNKED) {
-      // a thread walks a channel's rows in order and carries the product of its gates
-      for (int e = tid; e < DKP; e += blockDim.x) {
-        float b = bs[e];
-        const int c = h * dk + e;
-        const float low = e < dk ? a.lower[c] : 0.f, bias = e < dk ? a.f_bias[c] : 0.f;
-        for (int tt = 0; tt < nt; ++tt) {
-          float q = 0.f, f = 1.f;
-          if (e < dk) {
-            const float* row = a.proj + (size_t)(first + t0 + tt) * a.ld;
-            const float zq = row[a.q_col + c];
-            q = zq * hg_sigmoid(zq);
-            f = low + (1.0f - low) * hg_sigmoid(row[a.f_col + c] + bias);
-            b *= f;
-            if (c0 == 0) a.qb[((size_t)(first + t0 + tt) * a.H + h) * dk + e] = q * b;
-          }
-          qs[tt][e] = q;
-          fs[tt][e] = f;
-        }
-        bs[e] = b;
-      }
-    } else {
     for (int i = tid; i < nt * DKP; i += blockDim.x) {
       const int tt = i / DKP, e = i % DKP;
       float q = 0.f, f = 1.f;
@@ -147,55 +128,79 @@ __global__ void __launch_bounds__(HG_COLS* HG_LANES) hgrn2_scan_kernel(const Hgr
       qs[tt][e] = q;
       fs[tt][e] = f;
     }
-    }
-    for (int i = tid; i < nt * HG_COLS; i += blockDim.x) {
-      const int tt = i / HG_COLS, c = c0 + i % HG_COLS;
-      vs[tt][i % HG_COLS] = c < dv ? a.proj[(size_t)(first + t0 + tt) * a.ld + a.v_col + h * dv + c] : 0.f;
+    for (int i = tid; i < nt * BC; i += blockDim.x) {
+      const int tt = i / BC, c = c0 + i % BC;
+      vs[tt][i % BC] = c < dv ? a.proj[(size_t)(first + t0 + tt) * a.ld + a.v_col + h * dv + c] : 0.f;
     }
     __syncthreads();
+    if (CHUNKED) {
+      // a thread walks a channel's staged rows in order and carries the product of its gates
+      for (int e = tid; e < dk; e += blockDim.x) {
+        float b = bs[e];
+        for (int tt = 0; tt < nt; ++tt) {
+          b *= fs[tt][e];
+          if (c0 == 0) a.qb[((size_t)(first + t0 + tt) * a.H + h) * dk + e] = qs[tt][e] * b;
+        }
+        bs[e] = b;
+      }
+    }
     for (int tt = 0; tt < nt; ++tt) {
-      const float v = vs[tt][tid / HG_LANES];
-      float acc = 0.f;
+      float v[CPT], acc[CPT];
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) v[c] = vs[tt][(tid / HG_LANES) * CPT + c], acc[c] = 0.f;
       if (KPL % 4 == 0) {
 #pragma unroll
         for (int r = 0; r < KPL; r += 4) {
           const float4 f4 = *reinterpret_cast<const float4*>(&fs[tt][hg_row<KPL>(lane, r)]);
           const float4 q4 = *reinterpret_cast<const float4*>(&qs[tt][hg_row<KPL>(lane, r)]);
-          S[r] = fmaf(f4.x, S[r], (1.0f - f4.x) * v);
-          S[r + 1] = fmaf(f4.y, S[r + 1], (1.0f - f4.y) * v);
-          S[r + 2] = fmaf(f4.z, S[r + 2], (1.0f - f4.z) * v);
-          S[r + 3] = fmaf(f4.w, S[r + 3], (1.0f - f4.w) * v);
-          acc = fmaf(S[r], q4.x, acc);
-          acc = fmaf(S[r + 1], q4.y, acc);
-          acc = fmaf(S[r + 2], q4.z, acc);
-          acc = fmaf(S[r + 3], q4.w, acc);
+#pragma unroll
+          for (int c = 0; c < CPT; ++c) {
+            S[c][r] = fmaf(f4.x, S[c][r], (1.0f - f4.x) * v[c]);
+            S[c][r + 1] = fmaf(f4.y, S[c][r + 1], (1.0f - f4.y) * v[c]);
+            S[c][r + 2] = fmaf(f4.z, S[c][r + 2], (1.0f - f4.z) * v[c]);
+            S[c][r + 3] = fmaf(f4.w, S[c][r + 3], (1.0f - f4.w) * v[c]);
+            acc[c] = fmaf(S[c][r], q4.x, acc[c]);
+            acc[c] = fmaf(S[c][r + 1], q4.y, acc[c]);
+            acc[c] = fmaf(S[c][r + 2], q4.z, acc[c]);
+            acc[c] = fmaf(S[c][r + 3], q4.w, acc[c]);
+          }
         }
       } else {
 #pragma unroll
         for (int r = 0; r < KPL; ++r) {
           const int i = hg_row<KPL>(lane, r);
-          const float f = fs[tt][i];
-          S[r] = fmaf(f, S[r], (1.0f - f) * v);
-          acc = fmaf(S[r], qs[tt][i], acc);
+          const float f = fs[tt][i], q = qs[tt][i];
+#pragma unroll
+          for (int c = 0; c < CPT; ++c) {
+            S[c][r] = fmaf(f, S[c][r], (1.0f - f) * v[c]);
+            acc[c] = fmaf(S[c][r], q, acc[c]);
+          }
         }
       }
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-      if (lane == 0 && live) a.o[((size_t)(first + t0 + tt) * a.H + h) * dv + col] = acc;
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) {
+        acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], 1);
+        acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], 2);
+        acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], 4);
+        if (lane == 0 && cb + c < dv) a.o[((size_t)(first + t0 + tt) * a.H + h) * dv + cb + c] = acc[c];
+      }
     }
   }
   pdl_launch_dependents_if_large();
-  if (sp && live) {
+  if (sp) {
 #pragma unroll
-    for (int r = 0; r < KPL; ++r) {
-      const int i = hg_row<KPL>(lane, r);
-      if (i < dk) sp[(size_t)i * dv + col] = S[r];
-    }
+    for (int c = 0; c < CPT; ++c)
+#pragma unroll
+      for (int r = 0; r < KPL; ++r) {
+        const int i = hg_row<KPL>(lane, r);
+        if (i < dk && cb + c < dv) sp[(size_t)i * dv + cb + c] = S[c][r];
+      }
   }
-  if (CHUNKED && c0 == 0)       // (bs was last written before the last stage's barrier)
+  if (CHUNKED && c0 == 0) {
+    __syncthreads();            // (the last stage's products are in bs)
     for (int e = tid; e < dk; e += blockDim.x)
       a.chunk_decay[(hg_entry(seq_first, z, seq) * a.H + h) * (size_t)dk + e] = bs[e];
+  }
 }
 
 // The states at the chunks' starts: a thread owns one element of a (sequence, head)'s matrix,
@@ -314,21 +319,32 @@ static bool hg_chunked(const Hgrn2Args& a) {
   return a.max_rows >= HG_CHUNK_MIN && a.qb && a.chunk_state && a.chunk_decay;
 }
 
-template <int KPL>
-static int launch_scan(const Hgrn2Args& a, cudaStream_t s) {
-  const int col_tiles = (a.dv + HG_COLS - 1) / HG_COLS;
+template <int KPL, int CPT>
+static int launch_scan_cols(const Hgrn2Args& a, cudaStream_t s) {
+  const int col_tiles = (a.dv + HG_COLS * CPT - 1) / (HG_COLS * CPT);
   if (!hg_chunked(a))
-    return gb_launch(hgrn2_scan_kernel<KPL, false>, dim3(a.H, a.n_seqs, col_tiles), dim3(HG_COLS * HG_LANES),
-                     0, s, a);
+    return gb_launch(hgrn2_scan_kernel<KPL, CPT, false>, dim3(a.H, a.n_seqs, col_tiles),
+                     dim3(HG_COLS * HG_LANES), 0, s, a);
   const int chunks = (a.max_rows + HG_CHUNK - 1) / HG_CHUNK;
   if ((long long)col_tiles * chunks > 65535) return GB_ERR_UNSUPPORTED;
-  int e = gb_launch(hgrn2_scan_kernel<KPL, true>, dim3(a.H, a.n_seqs, col_tiles * chunks),
+  int e = gb_launch(hgrn2_scan_kernel<KPL, CPT, true>, dim3(a.H, a.n_seqs, col_tiles * chunks),
                     dim3(HG_COLS * HG_LANES), 0, s, a);
   if (e) return e;
   const size_t per = (size_t)a.dk * a.dv;
   e = gb_launch(hgrn2_prefix_kernel, dim3((unsigned)((per + 255) / 256), a.H, a.n_seqs), dim3(256), 0, s, a);
   if (e) return e;
   return gb_launch(hgrn2_cross_kernel, dim3(a.H, a.n_seqs, chunks * ((a.dv + 63) / 64)), dim3(256), 0, s, a);
+}
+
+// A thread owns several columns of S where a head is wide enough for that to leave blocks for
+// every SM (four columns of heads up to 128 elements, two of longer ones); a column's sums are
+// the same in every case.
+template <int KPL>
+static int launch_scan(const Hgrn2Args& a, cudaStream_t s) {
+  constexpr int WIDE = KPL <= 16 ? 4 : 2;
+  // (a step of few rows is the time to bring the state in and out: many small blocks do that best)
+  if (a.dv >= HG_COLS * WIDE && a.max_rows >= HG_STAGE) return launch_scan_cols<KPL, WIDE>(a, s);
+  return launch_scan_cols<KPL, 1>(a, s);
 }
 
 template <typename T>
