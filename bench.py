@@ -229,20 +229,20 @@ def zutazen_config(size: str) -> dict:
 
 def mananex_config(size: str) -> dict:
     """The Mananex model of a size: the width, heads, head size, layers and vocabulary of
-    the Qwen3 model; every layer's mixer is attention (the Qwen3 model's heads, a quarter of
-    every head rotated, a window of 1,024 that keeps the first four tokens, sinks, a gate per
+    the Qwen3 model; every layer's mixer is attention (the Qwen3 model's heads, half of
+    every head rotated, a window of 1,024 that keeps the first eight tokens, sinks, a gate per
     head) beside forget-gate linear attention (half as many heads, keys of half the head
     size, values of the head size); every other layer has a dense feed-forward of the same
-    rows and the rest route three of eight experts of a quarter of the rows each; every
+    rows and the rest route two of eight experts of a quarter of the rows each; every
     sublayer's result passes a residual gate of the stream's width, and the stream is the
     depth average of all layers' results."""
     W, nq, nkv, D, I, L, V = DESIGN_SIZES[size]
-    left = dict(heads=nq, kv_heads=nkv, dim=D, vdim=D, scale=D ** -0.5, rot={"base": 500000.0, "dims": D // 4},
-                mask={"size": 1024, "keep_first": 4})
+    left = dict(heads=nq, kv_heads=nkv, dim=D, vdim=D, scale=D ** -0.5, rot={"base": 500000.0, "dims": D // 2},
+                mask={"size": 1024, "keep_first": 8})
     right = dict(heads=nq // 2, dim=D // 2, vdim=D)
     mixer = dict(left=left, right=right, left_scale=0.7, right_scale=1.1)
     dense = {"kind": "dense", "ff": I}
-    moe = {"kind": "moe", "expert": {"ff": I // 4 // 64 * 64}, "router": {"experts": 8, "top": 3}}
+    moe = {"kind": "moe", "expert": {"ff": I // 4 // 64 * 64}, "router": {"experts": 8, "top": 2}}
     layers = [dict(type="parallel", mixer=mixer, mlp=dense if i % 2 == 0 else moe) for i in range(L)]
     return dict(architecture="Mananex", vocab=V, width=W, norm={"eps": 1e-6}, layers=layers)
 

@@ -241,7 +241,7 @@ def _attention_plain(x, w, H, G, D, Dv, window, keep, rot_dims, positions=None, 
 
 ATT_SHAPES = [  # heads, kv heads, dim, vdim, window, kept, rotated
     (4, 2, 16, 16, 7, 2, 8), (2, 2, 64, 64, 64, 1, 64), (2, 1, 64, 64, 65, 64, 16), (2, 2, 128, 128, 63, 65, 32),
-    (3, 3, 40, 40, 10, 3, 40), (2, 1, 24, 8, 70, 5, 4), (2, 2, 16, 48, 1, 1, 0), (4, 4, 96, 96, 130, 70, 24),
+    (3, 3, 40, 40, 10, 3, 40), (2, 1, 24, 8, 70, 5, 4), (2, 2, 16, 48, 1, 1, 0), (4, 2, 96, 96, 130, 70, 32),
     (2, 2, 32, 32, 300, 4, 32), (2, 2, 32, 32, 5, 0, 6), (1, 1, 144, 16, 33, 2, 20)]
 
 
